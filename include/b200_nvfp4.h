@@ -1,0 +1,133 @@
+/*
+ * C ABI of libb200nvfp4.so: NVFP4 block-scaled dual GEMM and grouped GEMM for
+ * NVIDIA B200 (sm_100a).
+ *
+ * All pointers marked "device" are device addresses on `device`; the library
+ * never allocates or frees them.  Calls enqueue work on `stream` (a
+ * cudaStream_t passed as void*, NULL = default stream) and return without
+ * synchronising, like the reference's custom_kernel() entry points.
+ *
+ * Return value of every int function: 0 = success, < 0 = argument rejected on
+ * the host before any CUDA work (B200_E_*), > 0 = a CUDA runtime/driver error
+ * code (cudaError_t).  b200_last_error() describes the last non-zero return of
+ * the calling thread.
+ */
+#ifndef B200_NVFP4_H_
+#define B200_NVFP4_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_E_NULL (-1)      /* a required pointer is NULL                      */
+#define B200_E_SHAPE (-2)     /* m/n/k/l violate the divisibility rules          */
+#define B200_E_ALIGN (-3)     /* a pointer or pitch is not 16-byte aligned       */
+#define B200_E_WORKSPACE (-4) /* workspace too small or misaligned               */
+#define B200_E_VARIANT (-5)   /* unknown kernel variant                          */
+#define B200_E_DRIVER (-6)    /* CUDA driver entry point unavailable             */
+#define B200_E_LIMIT (-7)     /* size beyond a documented maximum                */
+
+/* Kernel variants (the `variant` argument of the *_ex entry points). */
+#define B200_VARIANT_AUTO 0       /* library picks by shape                            */
+#define B200_VARIANT_PERSISTENT 1 /* warp-specialised persistent kernel               */
+#define B200_VARIANT_SERIAL 2     /* one CTA per tile, single stage (bring-up / debug) */
+#define B200_VARIANT_SERIAL_2MMA 3/* as SERIAL but two N=128 MMAs per k-block          */
+#define B200_VARIANT_SPLITK 4     /* persistent kernel, k-range split over CTAs with an
+                                     fp32 partial-sum exchange before the epilogue     */
+
+/* Library version string, e.g. "b200nvfp4 0.1 (sm_100a)". */
+const char* b200_version(void);
+
+/* Message for the calling thread's last failing call ("" if none). */
+const char* b200_last_error(void);
+
+/*
+ * C[m, n, l] = silu(A . B1^T) * (A . B2^T), fp32 accumulation, fp16 output.
+ * Replaces custom_kernel(data) of the reference's dual GEMM
+ * (dual_gemm/submission.py:894-957, dual_gemm/dual_gemm_opt_cute.py:2706-2832).
+ *
+ *   a            device, [m, k/2, l] packed e2m1 (2 per byte, low nibble = even k),
+ *                K-major, batch stride m*k/2 bytes                    (data[0])
+ *   b1, b2       device, [n, k/2, l] packed e2m1, batch stride
+ *                b_batch_bytes (n*k/2 when 0)                          (data[1], data[2])
+ *   sfa          device, e4m3 scale factors of A in the permuted layout
+ *                (32,4,ceil(m/128),4,k/64,l)                           (data[6])
+ *   sfb1, sfb2   device, same layout for B1/B2 rows; batch stride
+ *                sfb_batch_bytes (ceil(n/128)*(k/64)*512 when 0)       (data[7], data[8])
+ *   c            device, fp16, element (i, j, b) at c[b*c_batch + i*ldc + j]
+ *                (c_batch = m*ldc when 0), written in place            (data[9])
+ *   m % 128 == 0, n % 128 == 0, k % 256 == 0, l >= 1; ldc % 8 == 0;
+ *   every pointer 16-byte aligned.
+ *
+ * `n` may be a column shard of a wider problem: pass the shard's rows of
+ * B1/B2, its scale-factor atoms and a `c` pointer offset to the shard's first
+ * column with `ldc` the full row pitch.
+ *
+ * status: device pointer to one uint32 the kernel ORs a non-zero code into if
+ * a bounded on-device wait gives up (0 stays 0 on success), or NULL to use a
+ * library-owned word readable with b200_read_status().
+ */
+int b200_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const void* sfa,
+                         const void* sfb1, const void* sfb2, void* c, int m, int n, int k, int l,
+                         int64_t ldc, void* stream, int device, uint32_t* status);
+
+/* Same, with explicit batch strides, kernel variant and (for
+ * B200_VARIANT_SPLITK, else may be NULL/0) an fp32 partial-sum workspace of
+ * b200_dual_splitk_workspace_bytes() bytes, 256-byte aligned. */
+int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const void* sfa,
+                            const void* sfb1, const void* sfb2, void* c, int m, int n, int k, int l,
+                            int64_t ldc, int64_t c_batch, int64_t b_batch_bytes,
+                            int64_t sfb_batch_bytes, int variant, void* workspace,
+                            size_t workspace_bytes, void* stream, int device, uint32_t* status);
+
+/* Bytes of workspace the split-k variant needs for an (m, n, k, l) problem. */
+size_t b200_dual_splitk_workspace_bytes(int m, int n, int k, int l);
+
+/*
+ * Grouped GEMM: for every group g, C_g[m_g, n_g] = A_g . B_g^T (fp16 output, no
+ * activation), all groups in one launch.  Replaces custom_kernel(data) of the
+ * reference's grouped GEMM (group_gemm/group_gemm_cute5_v2.py:4245-4424,
+ * group_gemm/group_gemm_cute4.py:1252-1399).
+ *
+ *   a[g], b[g], c[g]   host arrays of device pointers: A_g [m_g, k_g/2],
+ *                      B_g [n_g, k_g/2] packed e2m1, C_g [m_g, n_g] fp16 row-major
+ *                      (abc_tensors[g])
+ *   sfa[g], sfb[g]     device pointers to the permuted scale factors
+ *                      (sfasfb_reordered_tensors[g]); rows of SFA beyond m_g may
+ *                      hold anything
+ *   mnk                host array of 3*groups ints (m_g, n_g, k_g);
+ *                      m_g >= 0 (0 = group skipped), n_g % 128 == 0, k_g % 256 == 0
+ *                      (problem_sizes[g][0:3], l == 1)
+ *   workspace          device scratch of at least b200_grouped_workspace_bytes(groups)
+ *                      bytes, 256-byte aligned; holds the per-group descriptors the
+ *                      kernel indexes.  The library rewrites it only when the
+ *                      descriptors differ from what it last put there.
+ */
+int b200_grouped_gemm_nvfp4(int groups, const void* const* a, const void* const* b,
+                            const void* const* sfa, const void* const* sfb, void* const* c,
+                            const int* mnk, void* workspace, size_t workspace_bytes, void* stream,
+                            int device, uint32_t* status);
+
+/* Same with an explicit kernel variant (AUTO, PERSISTENT or SERIAL) and
+ * N-tile width (0 = auto, 128 or 256). */
+int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* const* b,
+                               const void* const* sfa, const void* const* sfb, void* const* c,
+                               const int* mnk, void* workspace, size_t workspace_bytes, int variant,
+                               int tile_n, void* stream, int device, uint32_t* status);
+
+size_t b200_grouped_workspace_bytes(int groups);
+
+/* Synchronise `stream`, copy the library-owned status word of `device` into
+ * *out and clear it. */
+int b200_read_status(int device, void* stream, uint32_t* out);
+
+/* Number of kernels this library has launched in the calling process. */
+uint64_t b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_NVFP4_H_ */

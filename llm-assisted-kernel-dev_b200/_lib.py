@@ -1,0 +1,85 @@
+"""ctypes binding of libb200nvfp4.so (the C ABI in include/b200_nvfp4.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is
+raised.  The library is looked for next to this file (built in-tree by
+``build.py``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200nvfp4.so")
+
+VARIANT_AUTO, VARIANT_PERSISTENT, VARIANT_SERIAL, VARIANT_SERIAL_2MMA, VARIANT_SPLITK = 0, 1, 2, 3, 4
+
+E_NULL, E_SHAPE, E_ALIGN, E_WORKSPACE, E_VARIANT, E_DRIVER, E_LIMIT = -1, -2, -3, -4, -5, -6, -7
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_i64 = ctypes.c_int64
+_sz = ctypes.c_size_t
+_u32p = ctypes.POINTER(ctypes.c_uint32)
+
+SIGNATURES = {
+    "b200_version": (ctypes.c_char_p, []),
+    "b200_last_error": (ctypes.c_char_p, []),
+    "b200_launch_count": (ctypes.c_uint64, []),
+    "b200_dual_gemm_nvfp4": (_i, [_vp] * 7 + [_i] * 4 + [_i64, _vp, _i, _vp]),
+    "b200_dual_gemm_nvfp4_ex": (_i, [_vp] * 7 + [_i] * 4 + [_i64] * 4 + [_i, _vp, _sz, _vp, _i, _vp]),
+    "b200_dual_splitk_workspace_bytes": (_sz, [_i] * 4),
+    "b200_grouped_gemm_nvfp4": (_i, [_i] + [_vp] * 6 + [_vp, _sz, _vp, _i, _vp]),
+    "b200_grouped_gemm_nvfp4_ex": (_i, [_i] + [_vp] * 6 + [_vp, _sz, _i, _i, _vp, _i, _vp]),
+    "b200_grouped_workspace_bytes": (_sz, [_i]),
+    "b200_read_status": (_i, [_i, _vp, _u32p]),
+}
+
+_lib = None
+
+
+class B200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"libb200nvfp4 error {code}: {message}")
+        self.code = code
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once) and declare every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python __graft_entry__.py` or "
+            f"`python llm-assisted-kernel-dev_b200/build.py` (needs nvcc). There is no CPU fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)        # AttributeError if a declared symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(code: int) -> None:
+    """Raise for a non-zero return: ValueError for rejected arguments (< 0),
+    B200Error for CUDA errors (> 0)."""
+    if code == 0:
+        return
+    msg = load().b200_last_error().decode()
+    if code < 0:
+        err = ValueError(f"libb200nvfp4 rejected the call ({code}): {msg}")
+        err.code = code
+        raise err
+    raise B200Error(code, msg)
+
+
+def read_status(device: int, stream: int = 0) -> int:
+    out = ctypes.c_uint32(0)
+    check(load().b200_read_status(device, stream, ctypes.byref(out)))
+    return out.value
+
+
+def launch_count() -> int:
+    return int(load().b200_launch_count())

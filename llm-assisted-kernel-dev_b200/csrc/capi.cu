@@ -1,0 +1,452 @@
+// Host side of libb200nvfp4.so: argument validation, tensor-map encoding,
+// launch configuration and the extern "C" entry points declared in
+// include/b200_nvfp4.h.  No torch types, no allocation of caller-visible memory.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/b200_nvfp4.h"
+#include "nvfp4_gemm_kernels.cuh"
+
+namespace b200 {
+namespace {
+
+thread_local std::string t_last_error;
+std::mutex g_mutex;
+uint64_t g_launches = 0;
+
+__device__ uint32_t g_device_status;   // library-owned status word (one per device)
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    t_last_error = buf;
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(static_cast<int>(e), "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+#define B200_CUDA(expr)                                              \
+    do {                                                             \
+        cudaError_t e_ = (expr);                                     \
+        if (e_ != cudaSuccess) return cuda_fail(e_, #expr);          \
+    } while (0)
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// --------------------------------------------------------------------------
+// Driver entry point for tensor-map encoding (no link-time libcuda dependency).
+// --------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int load_driver() {
+    if (g_encode) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+        cudaGetLastError();
+        return fail(B200_E_DRIVER, "cuTensorMapEncodeTiled is unavailable (no CUDA driver?)");
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return 0;
+}
+
+// Packed e2m1 operand [batches][rows][k/2] bytes -> 3-D map, box 128 B x 128 rows,
+// 128-byte swizzle, out-of-range rows read as zero.
+int encode_operand_map(CUtensorMap* map, const void* base, int rows, int k, int batches,
+                       long long batch_stride_bytes) {
+    if (rows <= 0) rows = 1;   // empty group: never dereferenced, keep the encoder happy
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(rows),
+                          static_cast<cuuint64_t>(batches)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(batch_stride_bytes)};
+    cuuint32_t box[3] = {128, 128, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200_E_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return 0;
+}
+
+// --------------------------------------------------------------------------
+// Per-device state
+// --------------------------------------------------------------------------
+struct DeviceState {
+    bool ready = false;
+    int sm_count = 0;
+    uint32_t* status = nullptr;
+};
+std::map<int, DeviceState> g_devices;
+
+template <typename K> int opt_in_smem(K kernel, uint32_t bytes) {
+    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+    return 0;
+}
+
+constexpr int kDualStages = 4;
+constexpr int kG128Stages = 6;
+constexpr int kG256Stages = 4;
+
+// Padded to more than half of the SM's shared memory so that only one serial CTA
+// (each allocates all 512 TMEM columns) is resident per SM.
+template <Mode M> constexpr uint32_t smem_bytes_serial() {
+    constexpr uint32_t need = 1024u + StageLayout<M>::kBytes + sizeof(ControlBlock);
+    return need > 120u * 1024u ? need : 120u * 1024u;
+}
+
+int device_state(int device, DeviceState** out) {
+    DeviceState& st = g_devices[device];
+    if (!st.ready) {
+        int rc = load_driver();
+        if (rc) return rc;
+        B200_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device));
+        B200_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&st.status), g_device_status));
+        B200_CUDA(cudaMemset(st.status, 0, sizeof(uint32_t)));
+        if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Dual, kDualStages>,
+                              smem_bytes_persistent<Mode::Dual, kDualStages>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Group128, kG128Stages>,
+                              smem_bytes_persistent<Mode::Group128, kG128Stages>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Group256, kG256Stages>,
+                              smem_bytes_persistent<Mode::Group256, kG256Stages>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Dual>, smem_bytes_serial<Mode::Dual>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group128>, smem_bytes_serial<Mode::Group128>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group256>, smem_bytes_serial<Mode::Group256>()))) return rc;
+        st.ready = true;
+    }
+    *out = &st;
+    return 0;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool switched = false;
+    int enter(int device) {
+        B200_CUDA(cudaGetDevice(&prev));
+        if (prev != device) {
+            B200_CUDA(cudaSetDevice(device));
+            switched = true;
+        }
+        return 0;
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(prev);
+    }
+};
+
+// --------------------------------------------------------------------------
+// Dual GEMM
+// --------------------------------------------------------------------------
+struct DualKey {
+    const void *a, *b1, *b2;
+    int m, n, k, l, device;
+    long long b_batch;
+    bool operator==(const DualKey& o) const {
+        return a == o.a && b1 == o.b1 && b2 == o.b2 && m == o.m && n == o.n && k == o.k && l == o.l &&
+               device == o.device && b_batch == o.b_batch;
+    }
+};
+struct DualMaps {
+    DualKey key;
+    CUtensorMap a, b1, b2;
+};
+std::vector<DualMaps> g_dual_cache;   // small most-recently-used list
+
+int validate_dual(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
+                  const void* sfb2, const void* c, int m, int n, int k, int l, long long ldc, long long c_batch,
+                  long long b_batch, long long sfb_batch) {
+    if (!a || !b1 || !b2 || !sfa || !sfb1 || !sfb2 || !c) return fail(B200_E_NULL, "dual gemm: NULL tensor pointer");
+    if (m <= 0 || n <= 0 || k <= 0 || l <= 0)
+        return fail(B200_E_SHAPE, "dual gemm: m, n, k, l must be positive (got %d %d %d %d)", m, n, k, l);
+    if (m % 128) return fail(B200_E_SHAPE, "dual gemm: m=%d is not a multiple of 128", m);
+    if (n % 128) return fail(B200_E_SHAPE, "dual gemm: n=%d is not a multiple of 128", n);
+    if (k % 256) return fail(B200_E_SHAPE, "dual gemm: k=%d is not a multiple of 256", k);
+    if (ldc < n || ldc % 8) return fail(B200_E_ALIGN, "dual gemm: ldc=%lld must be >= n and a multiple of 8", ldc);
+    if (c_batch % 8 || b_batch % 16 || sfb_batch % 16)
+        return fail(B200_E_ALIGN, "dual gemm: batch strides must keep 16-byte alignment");
+    if (!aligned16(a) || !aligned16(b1) || !aligned16(b2) || !aligned16(sfa) || !aligned16(sfb1) ||
+        !aligned16(sfb2) || !aligned16(c))
+        return fail(B200_E_ALIGN, "dual gemm: every tensor pointer must be 16-byte aligned");
+    return 0;
+}
+
+template <Mode M, int kStages, typename P>
+int launch_persistent(const P& prob, int units, int sm_count, int two_mma, cudaStream_t stream) {
+    const int grid = units < sm_count ? units : sm_count;
+    nvfp4_gemm_persistent<M, kStages><<<grid, 192, smem_bytes_persistent<M, kStages>(), stream>>>(prob, two_mma);
+    B200_CUDA(cudaGetLastError());
+    ++g_launches;
+    return 0;
+}
+
+template <Mode M, typename P> int launch_serial(const P& prob, int units, int two_mma, cudaStream_t stream) {
+    nvfp4_gemm_serial<M><<<units, 128, smem_bytes_serial<M>(), stream>>>(prob, two_mma);
+    B200_CUDA(cudaGetLastError());
+    ++g_launches;
+    return 0;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+const char* b200_version(void) { return "b200nvfp4 0.1 (sm_100a)"; }
+
+const char* b200_last_error(void) { return t_last_error.c_str(); }
+
+uint64_t b200_launch_count(void) { return g_launches; }
+
+size_t b200_dual_splitk_workspace_bytes(int m, int n, int k, int l) {
+    (void)k;
+    if (m <= 0 || n <= 0 || l <= 0) return 0;
+    return 0;
+}
+
+int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
+                            const void* sfb2, void* c, int m, int n, int k, int l, int64_t ldc, int64_t c_batch,
+                            int64_t b_batch_bytes, int64_t sfb_batch_bytes, int variant, void* workspace,
+                            size_t workspace_bytes, void* stream, int device, uint32_t* status) {
+    (void)workspace;
+    (void)workspace_bytes;
+    if (c_batch == 0) c_batch = static_cast<int64_t>(m) * ldc;
+    if (b_batch_bytes == 0) b_batch_bytes = static_cast<int64_t>(n) * (k / 2);
+    if (sfb_batch_bytes == 0) sfb_batch_bytes = static_cast<int64_t>(n / 128) * (k / 64) * 512;
+    int rc = validate_dual(a, b1, b2, sfa, sfb1, sfb2, c, m, n, k, l, ldc, c_batch, b_batch_bytes, sfb_batch_bytes);
+    if (rc) return rc;
+    if (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_SPLITK)
+        return fail(B200_E_VARIANT, "dual gemm: unknown variant %d", variant);
+    if (variant == B200_VARIANT_SPLITK) return fail(B200_E_VARIANT, "dual gemm: split-k variant not built");
+
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+
+    DenseProblem p;
+    memset(&p, 0, sizeof p);
+    DualKey key{a, b1, b2, m, n, k, l, device, b_batch_bytes};
+    const DualMaps* maps = nullptr;
+    for (const DualMaps& e : g_dual_cache)
+        if (e.key == key) { maps = &e; break; }
+    if (!maps) {
+        DualMaps fresh;
+        memset(&fresh, 0, sizeof fresh);
+        fresh.key = key;
+        if ((rc = encode_operand_map(&fresh.a, a, m, k, l, static_cast<long long>(m) * (k / 2)))) return rc;
+        if ((rc = encode_operand_map(&fresh.b1, b1, n, k, l, b_batch_bytes))) return rc;
+        if ((rc = encode_operand_map(&fresh.b2, b2, n, k, l, b_batch_bytes))) return rc;
+        if (g_dual_cache.size() >= 16) g_dual_cache.erase(g_dual_cache.begin());
+        g_dual_cache.push_back(fresh);
+        maps = &g_dual_cache.back();
+    }
+    p.map_a = maps->a;
+    p.map_b1 = maps->b1;
+    p.map_b2 = maps->b2;
+    p.sfa = static_cast<const uint8_t*>(sfa);
+    p.sfb1 = static_cast<const uint8_t*>(sfb1);
+    p.sfb2 = static_cast<const uint8_t*>(sfb2);
+    p.c = static_cast<__half*>(c);
+    p.ldc = ldc;
+    p.c_batch = c_batch;
+    p.sfa_batch = static_cast<long long>(m / 128) * (k / 64) * 512;
+    p.sfb_batch = sfb_batch_bytes;
+    p.m_tiles = m / 128;
+    p.n_tiles = n / 128;
+    p.k_tiles = k / 256;
+    p.batches = l;
+    p.total_tiles = p.m_tiles * p.n_tiles * l;
+    p.sf_k_atoms = k / 64;
+    p.k_splits = 1;
+    p.status = status ? status : st->status;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (variant) {
+        case B200_VARIANT_SERIAL:
+            return launch_serial<Mode::Dual>(p, p.total_tiles, 0, s);
+        case B200_VARIANT_SERIAL_2MMA:
+            return launch_serial<Mode::Dual>(p, p.total_tiles, 1, s);
+        default:
+            return launch_persistent<Mode::Dual, kDualStages>(p, p.total_tiles, st->sm_count, 0, s);
+    }
+}
+
+int b200_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
+                         const void* sfb2, void* c, int m, int n, int k, int l, int64_t ldc, void* stream,
+                         int device, uint32_t* status) {
+    return b200_dual_gemm_nvfp4_ex(a, b1, b2, sfa, sfb1, sfb2, c, m, n, k, l, ldc, 0, 0, 0, B200_VARIANT_AUTO,
+                                   nullptr, 0, stream, device, status);
+}
+
+size_t b200_grouped_workspace_bytes(int groups) {
+    if (groups <= 0) return 0;
+    return static_cast<size_t>(groups) * sizeof(GroupEntry);
+}
+
+}  // extern "C"
+
+namespace b200 {
+namespace {
+// What the library last wrote to a given workspace address, so identical
+// descriptor tables are not rebuilt or re-uploaded on every call.
+struct WorkspaceImage {
+    std::vector<uint8_t> key;       // raw call arguments
+    int total_tiles = 0;
+    int tile_n = 0;
+};
+std::map<std::pair<int, const void*>, WorkspaceImage> g_workspaces;
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
+int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* const* b, const void* const* sfa,
+                               const void* const* sfb, void* const* c, const int* mnk, void* workspace,
+                               size_t workspace_bytes, int variant, int tile_n, void* stream, int device,
+                               uint32_t* status) {
+    if (groups <= 0) return fail(B200_E_SHAPE, "grouped gemm: groups=%d must be positive", groups);
+    if (!a || !b || !sfa || !sfb || !c || !mnk) return fail(B200_E_NULL, "grouped gemm: NULL argument array");
+    if (variant != B200_VARIANT_AUTO && variant != B200_VARIANT_PERSISTENT && variant != B200_VARIANT_SERIAL)
+        return fail(B200_E_VARIANT, "grouped gemm: unknown variant %d", variant);
+    if (tile_n != 0 && tile_n != 128 && tile_n != 256)
+        return fail(B200_E_VARIANT, "grouped gemm: tile_n=%d must be 0, 128 or 256", tile_n);
+    bool all_n256 = true;
+    long long tiles128 = 0;
+    for (int g = 0; g < groups; ++g) {
+        const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
+        if (m < 0 || n <= 0 || k <= 0)
+            return fail(B200_E_SHAPE, "grouped gemm: group %d has invalid shape (%d, %d, %d)", g, m, n, k);
+        if (n % 128) return fail(B200_E_SHAPE, "grouped gemm: group %d n=%d is not a multiple of 128", g, n);
+        if (k % 256) return fail(B200_E_SHAPE, "grouped gemm: group %d k=%d is not a multiple of 256", g, k);
+        if (m == 0) continue;
+        if (!a[g] || !b[g] || !sfa[g] || !sfb[g] || !c[g])
+            return fail(B200_E_NULL, "grouped gemm: group %d has a NULL tensor pointer", g);
+        if (!aligned16(a[g]) || !aligned16(b[g]) || !aligned16(sfa[g]) || !aligned16(sfb[g]) || !aligned16(c[g]))
+            return fail(B200_E_ALIGN, "grouped gemm: group %d has a pointer that is not 16-byte aligned", g);
+        if (n % 256) all_n256 = false;
+        tiles128 += static_cast<long long>((m + 127) / 128) * (n / 128);
+    }
+    if (!workspace) return fail(B200_E_WORKSPACE, "grouped gemm: workspace is NULL");
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u)
+        return fail(B200_E_WORKSPACE, "grouped gemm: workspace must be 256-byte aligned");
+    if (workspace_bytes < b200_grouped_workspace_bytes(groups))
+        return fail(B200_E_WORKSPACE, "grouped gemm: workspace has %zu bytes, %zu needed", workspace_bytes,
+                    b200_grouped_workspace_bytes(groups));
+    if (tiles128 == 0) return 0;   // every group is empty: nothing to do
+
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    int rc;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+
+    // Wide tiles halve the A traffic per flop; keep 128-wide tiles when they are
+    // needed to give every SM work or when some n is not a multiple of 256.
+    if (tile_n == 0) tile_n = (all_n256 && tiles128 / 2 >= 2LL * st->sm_count) ? 256 : 128;
+
+    std::vector<uint8_t> key(sizeof(int) * 2 + groups * (5 * sizeof(void*) + 3 * sizeof(int)));
+    {
+        uint8_t* w = key.data();
+        auto put = [&w](const void* src, size_t nbytes) { memcpy(w, src, nbytes); w += nbytes; };
+        put(&groups, sizeof(int));
+        put(&tile_n, sizeof(int));
+        put(a, groups * sizeof(void*));
+        put(b, groups * sizeof(void*));
+        put(sfa, groups * sizeof(void*));
+        put(sfb, groups * sizeof(void*));
+        put(c, groups * sizeof(void*));
+        put(mnk, groups * 3 * sizeof(int));
+    }
+    WorkspaceImage& img = g_workspaces[{device, workspace}];
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (img.key != key) {
+        std::vector<GroupEntry> table(groups);
+        memset(table.data(), 0, groups * sizeof(GroupEntry));
+        int tile_begin = 0;
+        for (int g = 0; g < groups; ++g) {
+            const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
+            GroupEntry& e = table[g];
+            e.m = m;
+            e.n = n;
+            e.k_tiles = k / 256;
+            e.m_tiles = (m + 127) / 128;
+            e.n_tiles = (n + tile_n - 1) / tile_n;
+            e.tile_begin = tile_begin;
+            e.sf_k_atoms = k / 64;
+            e.sfb_row_atoms = n / 128;
+            e.ldc = n;
+            tile_begin += e.m_tiles * e.n_tiles;
+            if (m == 0) continue;
+            e.sfa = static_cast<const uint8_t*>(sfa[g]);
+            e.sfb = static_cast<const uint8_t*>(sfb[g]);
+            e.c = static_cast<__half*>(c[g]);
+            if ((rc = encode_operand_map(&e.map_a, a[g], m, k, 1, static_cast<long long>(m) * (k / 2)))) return rc;
+            if ((rc = encode_operand_map(&e.map_b, b[g], n, k, 1, static_cast<long long>(n) * (k / 2)))) return rc;
+        }
+        // Pageable source: the runtime stages the bytes before returning, so
+        // `table` may go out of scope while the copy is still queued.
+        B200_CUDA(cudaMemcpyAsync(workspace, table.data(), groups * sizeof(GroupEntry), cudaMemcpyHostToDevice, s));
+        img.key = key;
+        img.total_tiles = tile_begin;
+        img.tile_n = tile_n;
+        if (g_workspaces.size() > 256) {   // bound the bookkeeping
+            WorkspaceImage keep = img;
+            g_workspaces.clear();
+            g_workspaces[{device, workspace}] = keep;
+        }
+    }
+    const WorkspaceImage& cur = g_workspaces[{device, workspace}];
+    GroupedProblem p;
+    p.groups = static_cast<const GroupEntry*>(workspace);
+    p.num_groups = groups;
+    p.total_tiles = cur.total_tiles;
+    p.status = status ? status : st->status;
+    if (variant == B200_VARIANT_SERIAL) {
+        return cur.tile_n == 256 ? launch_serial<Mode::Group256>(p, p.total_tiles, 0, s)
+                                 : launch_serial<Mode::Group128>(p, p.total_tiles, 0, s);
+    }
+    return cur.tile_n == 256
+               ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s)
+               : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s);
+}
+
+int b200_grouped_gemm_nvfp4(int groups, const void* const* a, const void* const* b, const void* const* sfa,
+                            const void* const* sfb, void* const* c, const int* mnk, void* workspace,
+                            size_t workspace_bytes, void* stream, int device, uint32_t* status) {
+    return b200_grouped_gemm_nvfp4_ex(groups, a, b, sfa, sfb, c, mnk, workspace, workspace_bytes, B200_VARIANT_AUTO,
+                                      0, stream, device, status);
+}
+
+int b200_read_status(int device, void* stream, uint32_t* out) {
+    if (!out) return fail(B200_E_NULL, "read_status: out is NULL");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    int rc;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B200_CUDA(cudaStreamSynchronize(s));
+    B200_CUDA(cudaMemcpy(out, st->status, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    if (*out) B200_CUDA(cudaMemset(st->status, 0, sizeof(uint32_t)));
+    return 0;
+}
+
+}  // extern "C"

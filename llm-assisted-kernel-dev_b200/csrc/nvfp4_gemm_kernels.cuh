@@ -1,0 +1,574 @@
+// NVFP4 block-scaled GEMM kernels for sm_100a.
+//
+// One kernel body serves three "modes":
+//   Dual      C = silu(A.B1^T) * (A.B2^T)   (reference kernels K1/K2:
+//             dual_gemm/submission.py:45-612, dual_gemm/dual_gemm_opt_cute.py:940-2107)
+//   Group128  C_g = A_g.B_g^T, 128x128 output tiles      (reference K5:
+//   Group256  C_g = A_g.B_g^T, 128x256 output tiles       group_gemm/group_gemm_cute5_v2.py:713-1747)
+//
+// Data path per 256-wide k-tile: TMA (128-byte-swizzled boxes of packed e2m1
+// bytes) + bulk copies of 2 KiB scale-factor chunks -> shared memory ring ->
+// tcgen05.cp (scale factors into TMEM) -> tcgen05.mma kind::mxf4nvf4.block_scale,
+// fp32 accumulator in TMEM -> tcgen05.ld -> epilogue -> st.global.
+//
+// In Dual mode the B1 and B2 tiles sit back to back in one stage, so a single
+// N=256 MMA per 64-k block produces both products (A and its scale factors are
+// staged once): accumulator columns [0,128) = A.B1^T, [128,256) = A.B2^T.
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+
+constexpr int kTileM = 128;
+constexpr int kTileK = 256;                     // e2m1 elements per k-tile (128 bytes per row)
+constexpr int kKBlocks = 4;                     // 64-element MMA k-blocks per k-tile
+constexpr uint32_t kOperandTileBytes = 128 * 128;  // 128 rows x 128 bytes
+constexpr uint32_t kSfChunkBytes = 2048;        // 128 rows x 16 scale factors (4 atoms of 512 B)
+constexpr uint32_t kSfAtomBytes = 512;
+constexpr uint32_t kTmemColumns = 512;
+
+// Status bits ORed into the status word when a bounded wait gives up.
+constexpr uint32_t kStatusProducerWait = 0x1;
+constexpr uint32_t kStatusMmaWaitFull = 0x2;
+constexpr uint32_t kStatusMmaWaitAcc = 0x4;
+constexpr uint32_t kStatusEpilogueWait = 0x8;
+constexpr uint32_t kStatusSerialWait = 0x10;
+constexpr uint32_t kStatusSplitKWait = 0x20;
+
+enum class Mode { Dual, Group128, Group256 };
+
+template <Mode M> struct ModeTraits;
+template <> struct ModeTraits<Mode::Dual> {
+    static constexpr int kMmaN = 256;       // accumulator columns
+    static constexpr int kOutCols = 128;    // output columns per tile
+    static constexpr bool kSilu = true;
+    static constexpr bool kHasBHi = true;
+};
+template <> struct ModeTraits<Mode::Group128> {
+    static constexpr int kMmaN = 128;
+    static constexpr int kOutCols = 128;
+    static constexpr bool kSilu = false;
+    static constexpr bool kHasBHi = false;
+};
+template <> struct ModeTraits<Mode::Group256> {
+    static constexpr int kMmaN = 256;
+    static constexpr int kOutCols = 256;
+    static constexpr bool kSilu = false;
+    static constexpr bool kHasBHi = true;
+};
+
+// ---------------------------------------------------------------------------
+// Problem descriptions
+// ---------------------------------------------------------------------------
+// Dual GEMM: lives in kernel parameter space (tensor maps need 64-byte alignment).
+struct alignas(64) DenseProblem {
+    CUtensorMap map_a, map_b1, map_b2;   // 3-D {k/2 bytes, rows, batch}, box {128, 128, 1}
+    const uint8_t* sfa;
+    const uint8_t* sfb1;
+    const uint8_t* sfb2;
+    __half* c;
+    long long ldc, c_batch;              // elements
+    long long sfa_batch, sfb_batch;      // bytes
+    float* splitk_ws;                    // fp32 partial sums (split-k variant only)
+    uint32_t* splitk_flags;              // one arrival counter per output tile
+    int m_tiles, n_tiles, k_tiles, batches;
+    int total_tiles;                     // m_tiles * n_tiles * batches
+    int sf_k_atoms;                      // k / 64
+    int k_splits;                        // 1 unless split-k
+    uint32_t* status;
+};
+
+// Grouped GEMM: one entry per group in device memory (the workspace).
+struct alignas(128) GroupEntry {
+    CUtensorMap map_a, map_b;            // 3-D {k/2 bytes, rows, 1}
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    __half* c;
+    long long ldc;
+    int m, n, k_tiles, m_tiles;
+    int n_tiles, tile_begin, sf_k_atoms, sfb_row_atoms;
+    int pad[8];
+};
+static_assert(sizeof(GroupEntry) == 384, "GroupEntry layout");
+
+struct GroupedProblem {
+    const GroupEntry* groups;
+    int num_groups;
+    int total_tiles;
+    uint32_t* status;
+};
+
+// One unit of work: a 128-row output tile.
+struct Work {
+    const void* map_a;
+    const void* map_blo;
+    const void* map_bhi;
+    const uint8_t* sfa;      // first 2 KiB chunk (k-tile 0) of this row block
+    const uint8_t* sfblo;
+    const uint8_t* sfbhi;
+    __half* c;               // &C(m0, n0)
+    long long ldc;
+    int a_row, blo_row, bhi_row, batch;
+    int rows_valid, cols_valid;
+    int k_tile_begin, k_tile_count;
+    int group;               // grouped modes: index of the group (for tensor-map acquire)
+    int tile;                // linear output-tile index (split-k bookkeeping)
+    int split;               // which k-split this unit is
+};
+
+template <Mode M> struct Scheduler;
+
+template <> struct Scheduler<Mode::Dual> {
+    using Params = DenseProblem;
+    __device__ static int total_units(const Params& p) { return p.total_tiles * p.k_splits; }
+    // Units are ordered split-major inside a tile so the CTAs that share a tile
+    // run in the same wave; tiles are ordered m-fastest inside an n panel.
+    __device__ static Work get(const Params& p, int unit, int& /*cursor*/) {
+        Work w;
+        const int split = unit % p.k_splits;
+        const int tile = unit / p.k_splits;
+        const int m_blk = tile % p.m_tiles;
+        const int t = tile / p.m_tiles;
+        const int n_blk = t % p.n_tiles;
+        const int b = t / p.n_tiles;
+        w.map_a = &p.map_a;
+        w.map_blo = &p.map_b1;
+        w.map_bhi = &p.map_b2;
+        w.a_row = m_blk * kTileM;
+        w.blo_row = w.bhi_row = n_blk * 128;
+        w.batch = b;
+        const long long sf_row = static_cast<long long>(p.sf_k_atoms) * kSfAtomBytes;
+        w.sfa = p.sfa + b * p.sfa_batch + m_blk * sf_row;
+        w.sfblo = p.sfb1 + b * p.sfb_batch + n_blk * sf_row;
+        w.sfbhi = p.sfb2 + b * p.sfb_batch + n_blk * sf_row;
+        w.ldc = p.ldc;
+        w.c = p.c + b * p.c_batch + static_cast<long long>(m_blk) * kTileM * p.ldc + n_blk * 128;
+        w.rows_valid = kTileM;
+        w.cols_valid = 128;
+        const int per = (p.k_tiles + p.k_splits - 1) / p.k_splits;
+        w.k_tile_begin = split * per;
+        w.k_tile_count = min(per, p.k_tiles - w.k_tile_begin);
+        w.group = 0;
+        w.tile = tile;
+        w.split = split;
+        return w;
+    }
+};
+
+template <Mode M> struct GroupScheduler {
+    using Params = GroupedProblem;
+    static constexpr int kBN = ModeTraits<M>::kOutCols;
+    __device__ static int total_units(const Params& p) { return p.total_tiles; }
+    // `cursor` remembers the group of the previous (smaller) tile id so the
+    // search is a short forward scan; groups with zero tiles are stepped over.
+    __device__ static Work get(const Params& p, int unit, int& cursor) {
+        int g = cursor;
+        const GroupEntry* e = p.groups + g;
+        while (g + 1 < p.num_groups && unit >= e->tile_begin + e->m_tiles * e->n_tiles) {
+            ++g;
+            ++e;
+        }
+        cursor = g;
+        const int local = unit - e->tile_begin;
+        const int m_blk = local % e->m_tiles;   // m fastest: neighbours share a B panel
+        const int n_blk = local / e->m_tiles;
+        Work w;
+        w.map_a = &e->map_a;
+        w.map_blo = w.map_bhi = &e->map_b;
+        w.a_row = m_blk * kTileM;
+        w.blo_row = n_blk * kBN;
+        w.bhi_row = n_blk * kBN + 128;
+        w.batch = 0;
+        const long long sf_row = static_cast<long long>(e->sf_k_atoms) * kSfAtomBytes;
+        const int lo_atom = n_blk * (kBN / 128);
+        const int hi_atom = min(lo_atom + 1, e->sfb_row_atoms - 1);
+        w.sfa = e->sfa + m_blk * sf_row;
+        w.sfblo = e->sfb + lo_atom * sf_row;
+        w.sfbhi = e->sfb + hi_atom * sf_row;
+        w.ldc = e->ldc;
+        w.c = e->c + static_cast<long long>(m_blk) * kTileM * e->ldc + n_blk * kBN;
+        w.rows_valid = min(kTileM, e->m - m_blk * kTileM);
+        w.cols_valid = min(kBN, e->n - n_blk * kBN);
+        w.k_tile_begin = 0;
+        w.k_tile_count = e->k_tiles;
+        w.group = g;
+        w.tile = unit;
+        w.split = 0;
+        return w;
+    }
+};
+template <> struct Scheduler<Mode::Group128> : GroupScheduler<Mode::Group128> {};
+template <> struct Scheduler<Mode::Group256> : GroupScheduler<Mode::Group256> {};
+
+// ---------------------------------------------------------------------------
+// Shared-memory stage and TMEM column maps
+// ---------------------------------------------------------------------------
+template <Mode M> struct StageLayout {
+    using T = ModeTraits<M>;
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffBLo = kOperandTileBytes;
+    static constexpr uint32_t kOffBHi = 2 * kOperandTileBytes;   // directly after BLo: one descriptor spans 256 rows
+    static constexpr uint32_t kOffSfA = (T::kHasBHi ? 3 : 2) * kOperandTileBytes;
+    static constexpr uint32_t kOffSfBLo = kOffSfA + kSfChunkBytes;
+    static constexpr uint32_t kOffSfBHi = kOffSfBLo + kSfChunkBytes;
+    static constexpr uint32_t kBytes = kOffSfBLo + (T::kHasBHi ? 2 : 1) * kSfChunkBytes;  // multiple of 1024
+    static constexpr uint32_t kTxBytes = kBytes;
+};
+
+// TMEM columns.  N=256 accumulators: two buffers at columns 0 and 208 that share
+// columns [208,256); scale factors in the last 48 columns.  The epilogue drains
+// the shared columns first and hands them back before it does anything else, so
+// the next tile's MMAs overlap with the rest of the epilogue.
+// N=128 accumulators: two disjoint buffers at 0 and 128.
+template <Mode M> struct TmemMap {
+    using T = ModeTraits<M>;
+    static constexpr bool kOverlapped = (T::kMmaN == 256);
+    static constexpr uint32_t kAccStride = kOverlapped ? 208 : 128;
+    static constexpr uint32_t kSfA = kOverlapped ? 464 : 256;         // 4 columns per k-block
+    static constexpr uint32_t kSfB = kSfA + 16;                        // kMmaN/32 columns per k-block
+    static constexpr uint32_t kSfBPerBlock = T::kMmaN / 32;
+    static constexpr int kEarlyChunks = kOverlapped ? 3 : 0;          // 48 shared columns / 16
+};
+
+struct ControlBlock {
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t acc_full[2];
+    uint64_t acc_release[2];
+    uint64_t aux;
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+};
+
+template <Mode M, int kStages> constexpr uint32_t smem_bytes_persistent() {
+    return 1024u + kStages * StageLayout<M>::kBytes + sizeof(ControlBlock);
+}
+
+// ---------------------------------------------------------------------------
+// Role bodies shared by the persistent and the serial kernel
+// ---------------------------------------------------------------------------
+template <Mode M>
+__device__ __forceinline__ void issue_stage_loads(const Work& w, int kt, uint32_t stage, uint32_t bar) {
+    using L = StageLayout<M>;
+    mbar_arrive_expect_tx(bar, L::kTxBytes);
+    const int kbyte = kt * 128;
+    tma_load_3d(stage + L::kOffA, w.map_a, bar, kbyte, w.a_row, w.batch);
+    tma_load_3d(stage + L::kOffBLo, w.map_blo, bar, kbyte, w.blo_row, w.batch);
+    if constexpr (ModeTraits<M>::kHasBHi)
+        tma_load_3d(stage + L::kOffBHi, w.map_bhi, bar, kbyte, w.bhi_row, w.batch);
+    const long long sf_off = static_cast<long long>(kt) * kSfChunkBytes;
+    bulk_load(stage + L::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
+    bulk_load(stage + L::kOffSfBLo, w.sfblo + sf_off, kSfChunkBytes, bar);
+    if constexpr (ModeTraits<M>::kHasBHi)
+        bulk_load(stage + L::kOffSfBHi, w.sfbhi + sf_off, kSfChunkBytes, bar);
+}
+
+// Scale factors smem -> TMEM, then the four 64-k MMAs of one k-tile.
+// `two_mma`: issue two N=128 MMAs (B-lo, B-hi) instead of one N=256 MMA.
+template <Mode M>
+__device__ __forceinline__ void issue_stage_mma(uint32_t stage, uint32_t tmem_base, uint32_t acc_col,
+                                                bool first_k_tile, bool two_mma) {
+    using L = StageLayout<M>;
+    using T = ModeTraits<M>;
+    using TM = TmemMap<M>;
+#pragma unroll
+    for (int kb = 0; kb < kKBlocks; ++kb) {
+        tc_cp_32x128b_warpx4(tmem_base + TM::kSfA + 4 * kb, smem_desc_sf(stage + L::kOffSfA + kb * kSfAtomBytes));
+        tc_cp_32x128b_warpx4(tmem_base + TM::kSfB + TM::kSfBPerBlock * kb,
+                             smem_desc_sf(stage + L::kOffSfBLo + kb * kSfAtomBytes));
+        if constexpr (T::kHasBHi)
+            tc_cp_32x128b_warpx4(tmem_base + TM::kSfB + TM::kSfBPerBlock * kb + 4,
+                                 smem_desc_sf(stage + L::kOffSfBHi + kb * kSfAtomBytes));
+    }
+    const uint64_t adesc = smem_desc_sw128(stage + L::kOffA);
+    const uint64_t bdesc = smem_desc_sw128(stage + L::kOffBLo);
+#pragma unroll
+    for (int kb = 0; kb < kKBlocks; ++kb) {
+        const uint32_t acc = (first_k_tile && kb == 0) ? 0u : 1u;
+        const uint32_t sfa = tmem_base + TM::kSfA + 4 * kb;
+        const uint32_t sfb = tmem_base + TM::kSfB + TM::kSfBPerBlock * kb;
+        // +32 bytes along k inside the 128-byte swizzle atom = +2 in the address field
+        if (T::kHasBHi && two_mma) {
+            const uint64_t bdesc_hi = smem_desc_sw128(stage + L::kOffBHi);
+            tc_mma_mxf4nvf4(tmem_base + acc_col, adesc + 2 * kb, bdesc + 2 * kb, idesc_mxf4nvf4(128, 128), sfa,
+                            sfb, acc);
+            tc_mma_mxf4nvf4(tmem_base + acc_col + 128, adesc + 2 * kb, bdesc_hi + 2 * kb,
+                            idesc_mxf4nvf4(128, 128), sfa, sfb + 4, acc);
+        } else {
+            tc_mma_mxf4nvf4(tmem_base + acc_col, adesc + 2 * kb, bdesc + 2 * kb,
+                            idesc_mxf4nvf4(128, T::kMmaN), sfa, sfb, acc);
+        }
+    }
+}
+
+// Convert + store one 16-column chunk held by this thread (one output row).
+template <bool kSilu>
+__device__ __forceinline__ void store_chunk(__half* row_ptr, int chunk, const uint32_t (&x)[16],
+                                            const uint32_t (&y)[16]) {
+    uint32_t packed[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float a = __uint_as_float(x[2 * i]), b = __uint_as_float(x[2 * i + 1]);
+        if constexpr (kSilu) {
+            a = silu_mul(a, __uint_as_float(y[2 * i]));
+            b = silu_mul(b, __uint_as_float(y[2 * i + 1]));
+        }
+        packed[i] = pack_half2(a, b);
+    }
+    __half* dst = row_ptr + chunk * 16;
+    st_global_v4(dst, packed[0], packed[1], packed[2], packed[3]);
+    st_global_v4(dst + 8, packed[4], packed[5], packed[6], packed[7]);
+}
+
+// Epilogue of one tile for one warp (TMEM lane quadrant `quad`).  When the
+// accumulator buffers overlap, the chunks living in the shared columns are
+// pulled into registers first and `release` is signalled before any math.
+template <Mode M, int kBuf>
+__device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base, int quad, int lane,
+                                              uint32_t release_bar) {
+    using T = ModeTraits<M>;
+    using TM = TmemMap<M>;
+    constexpr int kChunks = T::kOutCols / 16;
+    constexpr int kEarly = TM::kEarlyChunks;
+    constexpr int kEarlyBegin = (kBuf == 0) ? kChunks - kEarly : 0;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
+    const int row = quad * 32 + lane;
+    const bool row_ok = row < w.rows_valid;
+    __half* row_ptr = w.c + static_cast<long long>(row) * w.ldc;
+
+    if constexpr (kEarly > 0) {
+        uint32_t ex[kEarly][16], ey[kEarly][16];
+#pragma unroll
+        for (int i = 0; i < kEarly; ++i) {
+            tc_ld_x16(acc + (kEarlyBegin + i) * 16, ex[i]);
+            if constexpr (T::kSilu) tc_ld_x16(acc + 128 + (kEarlyBegin + i) * 16, ey[i]);
+        }
+        tc_wait_ld();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(release_bar);
+#pragma unroll
+        for (int i = 0; i < kEarly; ++i) {
+            const int chunk = kEarlyBegin + i;
+            if (row_ok && chunk * 16 < w.cols_valid) store_chunk<T::kSilu>(row_ptr, chunk, ex[i], T::kSilu ? ey[i] : ex[i]);
+        }
+    }
+#pragma unroll
+    for (int chunk = 0; chunk < kChunks; ++chunk) {
+        if (kEarly > 0 && chunk >= kEarlyBegin && chunk < kEarlyBegin + kEarly) continue;
+        uint32_t x[16], y[16];
+        tc_ld_x16(acc + chunk * 16, x);
+        if constexpr (T::kSilu) tc_ld_x16(acc + 128 + chunk * 16, y);
+        tc_wait_ld();
+        if (row_ok && chunk * 16 < w.cols_valid) store_chunk<T::kSilu>(row_ptr, chunk, x, T::kSilu ? y : x);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Persistent warp-specialised kernel: 6 warps.
+//   warps 0-3  epilogue (TMEM lane quadrants 0-3)
+//   warp 4     TMEM allocation + MMA issue (one lane)
+//   warp 5     TMA producer (one lane)
+// CTA b walks work units b, b+grid, b+2*grid, ...
+// ---------------------------------------------------------------------------
+template <Mode M, int kStages>
+__global__ void __launch_bounds__(192, 1)
+nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, int two_mma) {
+    using L = StageLayout<M>;
+    using TM = TmemMap<M>;
+    using S = Scheduler<M>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    ControlBlock* ctl = reinterpret_cast<ControlBlock*>(smem_raw + (smem_base - smem_u32(smem_raw)) +
+                                                        kStages * L::kBytes);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(&ctl->full[s]), 1);
+            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl->acc_full[b]), 1);
+            mbar_init(smem_u32(&ctl->acc_release[b]), 4);
+        }
+        mbar_init(smem_u32(&ctl->aux), 1);
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(&ctl->tmem_base), kTmemColumns);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+    const int total = S::total_units(p);
+    volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+    if (warp == 5) {
+        // ------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            int cursor = 0, last_group = -1;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x) {
+                const Work w = S::get(p, unit, cursor);
+                if (M != Mode::Dual && w.group != last_group) {
+                    tensormap_acquire(w.map_a);
+                    tensormap_acquire(w.map_blo);
+                    last_group = w.group;
+                }
+                for (int i = 0; i < w.k_tile_count; ++i) {
+                    if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status, kStatusProducerWait)) {
+                        ok = false;
+                        break;
+                    }
+                    issue_stage_loads<M>(w, w.k_tile_begin + i, smem_base + s * L::kBytes, smem_u32(&ctl->full[s]));
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // error path only: give copies still in flight time to land
+                for (int i = 0; i < 64; ++i) __nanosleep(2000);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 4) {
+        // ------------------------------ MMA issuer
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            int cursor = 0, it = 0;
+            bool ok = true;
+            for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x, ++it) {
+                const Work w = S::get(p, unit, cursor);
+                if (it > 0) {
+                    const int j = it - 1;   // wait for hand-back number j
+                    if (!mbar_wait(smem_u32(&ctl->acc_release[j & 1]), (j >> 1) & 1, abort_flag, p.status,
+                                   kStatusMmaWaitAcc)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                }
+                const uint32_t acc_col = (it & 1) * TM::kAccStride;
+                for (int i = 0; i < w.k_tile_count; ++i) {
+                    if (!mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusMmaWaitFull)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    issue_stage_mma<M>(smem_base + s * L::kBytes, tmem_base, acc_col, i == 0, two_mma != 0);
+                    tc_commit(smem_u32(&ctl->empty[s]));   // frees the stage once these MMAs retire
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                }
+                if (ok) tc_commit(smem_u32(&ctl->acc_full[it & 1]));
+            }
+            // drain: every MMA issued above must retire before TMEM is freed
+            tc_commit(smem_u32(&ctl->aux));
+            mbar_wait(smem_u32(&ctl->aux), 0, abort_flag, p.status, kStatusMmaWaitAcc);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ epilogue warps 0-3
+        int cursor = 0, it = 0;
+        bool ok = true;
+        for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x, ++it) {
+            const Work w = S::get(p, unit, cursor);
+            const uint32_t release_bar = smem_u32(&ctl->acc_release[it & 1]);
+            if constexpr (!TM::kOverlapped) {
+                // disjoint buffers: hand-back number `it` says "tile it-1 is drained"
+                __syncwarp();
+                if (lane == 0) mbar_arrive(release_bar);
+            }
+            if (!mbar_wait(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
+                           kStatusEpilogueWait)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            if (it & 1)
+                epilogue_tile<M, 1>(w, tmem_base, warp, lane, release_bar);
+            else
+                epilogue_tile<M, 0>(w, tmem_base, warp, lane, release_bar);
+            tc_fence_before_sync();
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 4) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Serial kernel: one CTA (128 threads) per work unit, one stage, every step
+// waits for the previous one.  Slow by construction; exists to validate the
+// descriptors and layouts independently of the pipelined kernel.
+// ---------------------------------------------------------------------------
+template <Mode M>
+__global__ void __launch_bounds__(128, 1)
+nvfp4_gemm_serial(const __grid_constant__ typename Scheduler<M>::Params p, int two_mma) {
+    using L = StageLayout<M>;
+    using S = Scheduler<M>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    ControlBlock* ctl = reinterpret_cast<ControlBlock*>(smem_raw + (smem_base - smem_u32(smem_raw)) + L::kBytes);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&ctl->full[0]), 1);
+        mbar_init(smem_u32(&ctl->empty[0]), 1);
+        mbar_init(smem_u32(&ctl->acc_release[0]), 4);
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&ctl->tmem_base), kTmemColumns);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile uint32_t* abort_flag = &ctl->abort_flag;
+    int cursor = 0;
+    const int unit = blockIdx.x;
+    if (unit < S::total_units(p)) {
+        const Work w = S::get(p, unit, cursor);
+        if (threadIdx.x == 0) {
+            if (M != Mode::Dual) {
+                tensormap_acquire(w.map_a);
+                tensormap_acquire(w.map_blo);
+            }
+            uint32_t ph = 0;
+            for (int i = 0; i < w.k_tile_count; ++i, ph ^= 1u) {
+                issue_stage_loads<M>(w, w.k_tile_begin + i, smem_base, smem_u32(&ctl->full[0]));
+                if (!mbar_wait(smem_u32(&ctl->full[0]), ph, abort_flag, p.status, kStatusSerialWait)) break;
+                tc_fence_after_sync();
+                issue_stage_mma<M>(smem_base, tmem_base, 0, i == 0, two_mma != 0);
+                tc_commit(smem_u32(&ctl->empty[0]));
+                if (!mbar_wait(smem_u32(&ctl->empty[0]), ph, abort_flag, p.status, kStatusSerialWait)) break;
+            }
+        }
+        __syncwarp();
+        tc_fence_before_sync();
+        __syncthreads();
+        tc_fence_after_sync();
+        if (!*abort_flag) epilogue_tile<M, 0>(w, tmem_base, warp, lane, smem_u32(&ctl->acc_release[0]));
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+}  // namespace b200

@@ -1,0 +1,60 @@
+"""Sharding of the two problems over the GPUs of one node.
+
+No data-path collective is involved: the dual GEMM splits its output columns
+(rows of B1/B2 and their scale-factor atoms; A and its scale factors are
+replicated), the grouped GEMM assigns whole groups to ranks.  Each rank keeps
+its slice of C.
+"""
+from __future__ import annotations
+
+
+def column_range(n: int, rank: int, world: int) -> tuple[int, int]:
+    """Contiguous [begin, end) output columns of ``rank``; boundaries fall on
+    multiples of 128 so scale-factor atoms are never split.  The first
+    ``(n/128) % world`` ranks get one extra 128-column block."""
+    if n % 128:
+        raise ValueError(f"n={n} is not a multiple of 128")
+    blocks = n // 128
+    base, extra = divmod(blocks, world)
+    begin = rank * base + min(rank, extra)
+    end = begin + base + (1 if rank < extra else 0)
+    return begin * 128, end * 128
+
+
+def shard_dual_input(data, rank: int, world: int):
+    """View of the dual-GEMM 10-tuple restricted to this rank's output columns.
+    All returned tensors alias the originals (no copies); ``c`` keeps the full
+    row pitch.  Requires L == 1 (loop over batches otherwise)."""
+    a, b1, b2, sfa, sfb1, sfb2, sfa_p, sfb1_p, sfb2_p, c = data
+    if c.shape[2] != 1:
+        raise ValueError("column sharding of a batched problem: shard each batch separately")
+    n = c.shape[1]
+    lo, hi = column_range(n, rank, world)
+    blo, bhi = lo // 128, hi // 128
+    return (a, b1[lo:hi], b2[lo:hi], sfa, sfb1[lo:hi], sfb2[lo:hi], sfa_p,
+            sfb1_p[:, :, blo:bhi], sfb2_p[:, :, blo:bhi], c[:, lo:hi])
+
+
+def assign_groups(problem_sizes, world: int, balance: bool = False) -> list[list[int]]:
+    """Group indices owned by each rank.  Default: contiguous blocks of
+    ceil(G / world) groups.  ``balance=True``: longest-processing-time greedy
+    on m*n*k so ragged groups spread evenly."""
+    g = len(problem_sizes)
+    if not balance:
+        per = (g + world - 1) // world
+        return [list(range(r * per, min(g, (r + 1) * per))) for r in range(world)]
+    order = sorted(range(g), key=lambda i: -(problem_sizes[i][0] * problem_sizes[i][1] * problem_sizes[i][2]))
+    load = [0] * world
+    owned: list[list[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = load.index(min(load))
+        owned[r].append(i)
+        load[r] += problem_sizes[i][0] * problem_sizes[i][1] * problem_sizes[i][2]
+    return [sorted(x) for x in owned]
+
+
+def shard_grouped_input(data, rank: int, world: int, balance: bool = False):
+    """The grouped 4-tuple restricted to the groups this rank owns."""
+    abc, sfs, sfs_perm, sizes = data
+    mine = assign_groups(sizes, world, balance)[rank]
+    return ([abc[i] for i in mine], [sfs[i] for i in mine], [sfs_perm[i] for i in mine], [sizes[i] for i in mine])

@@ -1,0 +1,128 @@
+"""GPU parity: the CUDA grouped GEMM (through the C ABI) against the CPU oracle."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOL_NORTH_STAR = 1e-2
+TOL_REFERENCE = 1e-3
+V_AUTO, V_PERSISTENT, V_SERIAL = 0, 1, 2
+
+# utils/group_gemm/task.yml:47-56 (seed 1111)
+REFERENCE_TESTS = [
+    ([96, 128], [128, 256], [256, 512]),
+    ([256, 72], [512, 384], [256, 256]),
+    ([128, 128], [128, 256], [512, 256]),
+    ([80, 128, 256], [384, 256, 128], [256, 512, 256]),
+    ([64, 72, 96], [128, 384, 512], [512, 512, 256]),
+    ([64, 256, 128], [768, 128, 256], [512, 256, 512]),
+    ([128, 128, 64], [256, 512, 512], [768, 256, 768]),
+    ([128, 128, 128, 128], [128, 128, 128, 128], [512, 256, 512, 256]),
+    ([40, 56, 384, 512], [512, 384, 256, 128], [256, 256, 256, 256]),
+    ([512, 384, 256, 128], [256, 256, 256, 256], [512, 768, 512, 768]),
+]
+
+
+def _run(pkg, data, variant=V_AUTO, tile_n=0, canary=100.0):
+    for (_a, _b, c) in data[0]:
+        c.fill_(canary)
+    out = pkg.group_gemm.custom_kernel(data, variant=variant, tile_n=tile_n)
+    torch.cuda.synchronize()
+    assert all(o is c for o, (_a, _b, c) in zip(out, data[0]))
+    assert pkg._lib.read_status(torch.cuda.current_device()) == 0
+    return out
+
+
+def _check(oracle, data, out, tol):
+    cpu = ([tuple(t.cpu() for t in abc) for abc in data[0]], data[1])
+    want = oracle.grouped_gemm(cpu)
+    assert len(out) == len(want)
+    for g, (o, w) in enumerate(zip(out, want)):
+        problems = oracle.compare(o, w, tol, tol)
+        assert problems == [], (g, problems)
+
+
+@pytest.mark.parametrize("case", range(len(REFERENCE_TESTS)))
+@pytest.mark.parametrize("variant", [V_SERIAL, V_PERSISTENT])
+def test_reference_test_lists(pkg, oracle, case, variant):
+    m, n, k = REFERENCE_TESTS[case]
+    data = pkg.inputs.generate_grouped_input(m, n, k, len(m), 1111, dist="reference", device="cuda")
+    _check(oracle, data, _run(pkg, data, variant), TOL_REFERENCE)
+
+
+@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("variant", [V_SERIAL, V_PERSISTENT])
+def test_tile_widths(pkg, oracle, tile_n, variant):
+    # n = 384 with 256-wide tiles exercises the clipped second half-tile
+    m, n, k = [200, 64, 384], [512, 384, 256], [512, 256, 768]
+    data = pkg.inputs.generate_grouped_input(m, n, k, 3, 5, dist="uniform16", device="cuda")
+    _check(oracle, data, _run(pkg, data, variant, tile_n), TOL_NORTH_STAR)
+
+
+def test_empty_groups_are_skipped(pkg, oracle):
+    m, n, k = [0, 136, 0, 64, 0], [256, 256, 128, 384, 256], [256, 512, 256, 256, 512]
+    data = pkg.inputs.generate_grouped_input(m, n, k, 5, 9, dist="reference", device="cuda")
+    out = _run(pkg, data)
+    _check(oracle, data, out, TOL_REFERENCE)
+    assert out[0].shape == (0, 256, 1)
+
+
+def test_all_groups_empty_is_a_no_op(pkg):
+    data = pkg.inputs.generate_grouped_input([0, 0], [128, 256], [256, 256], 2, 1, device="cuda")
+    before = pkg._lib.launch_count()
+    pkg.group_gemm.custom_kernel(data)
+    assert pkg._lib.launch_count() == before
+
+
+def test_rows_beyond_m_are_not_written(pkg):
+    # C_g is allocated with guard rows after it: the kernel must not touch them
+    m, n, k = 72, 256, 256
+    data = pkg.inputs.generate_grouped_input([m], [n], [k], 1, 2, dist="reference", device="cuda")
+    (a, b, _c) = data[0][0]
+    big = torch.full((128, n, 1), 7.0, dtype=torch.float16, device="cuda")
+    data[0][0] = (a, b, big[:m])
+    pkg.group_gemm.custom_kernel(data)
+    torch.cuda.synchronize()
+    assert torch.all(big[m:] == 7.0)
+    assert not torch.all(big[:m] == 7.0)
+
+
+def test_known_answers(pkg):
+    kw = dict(unit_sfa=True, unit_sfb=True, device="cuda", fill_c=100.0)
+    data = pkg.inputs.generate_grouped_input([128], [128], [256], 1, 0, constant_a=True, constant_b=True, **kw)
+    assert torch.all(_run(pkg, data)[0] == 256.0)
+    data = pkg.inputs.generate_grouped_input([128], [256], [512], 1, 0, identity_a=True, identity_b=True, **kw)
+    out = _run(pkg, data)[0][:, :, 0].float().cpu()
+    assert torch.equal(out, torch.eye(128, 256))
+    data = pkg.inputs.generate_grouped_input([128], [128], [256], 1, 0, single_a=(3, 77, -1.5), constant_b=True, **kw)
+    out = _run(pkg, data)[0][:, :, 0].float().cpu()
+    want = torch.zeros(128, 128)
+    want[3] = -1.5
+    assert torch.equal(out, want)
+
+
+def test_benchmark_list_g8(pkg, oracle):
+    # utils/group_gemm/task.yml:59
+    m = [80, 176, 128, 72, 64, 248, 96, 160]
+    data = pkg.inputs.generate_grouped_input(m, [4096] * 8, [7168] * 8, 8, 1111, dist="reference", device="cuda")
+    _check(oracle, data, _run(pkg, data), TOL_REFERENCE)
+
+
+def test_moe_routing_shape_with_zero_counts(pkg, oracle):
+    # small cousin of the 64-expert MoE configuration: ragged counts incl. zeros
+    counts = pkg.inputs.moe_expert_counts(96, 16, 2, seed=4)
+    counts[3] = 0
+    data = pkg.inputs.generate_grouped_input(counts, [256] * 16, [512] * 16, 16, 3, dist="uniform16", device="cuda")
+    _check(oracle, data, _run(pkg, data), TOL_NORTH_STAR)
+
+
+def test_repeated_calls_reuse_descriptors(pkg, oracle):
+    m, n, k = [96, 128], [128, 256], [256, 512]
+    data = pkg.inputs.generate_grouped_input(m, n, k, 2, 1111, dist="reference", device="cuda")
+    first = [o.clone() for o in _run(pkg, data)]
+    second = _run(pkg, data)
+    for x, y in zip(first, second):
+        assert torch.equal(x, y)
+    other = pkg.inputs.generate_grouped_input(m, n, k, 2, 1153, dist="reference", device="cuda")
+    _check(oracle, other, _run(pkg, other), TOL_REFERENCE)
+    _check(oracle, data, _run(pkg, data), TOL_REFERENCE)
