@@ -1,0 +1,378 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 dual GEMM / grouped GEMM path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A "step" is one launch of the dual GEMM C = silu(A.B1^T) * (A.B2^T) on the
+SwiGLU-FFN shape M=8192, N=14336, K=4096 (NVFP4 operands, e4m3 scale factors per
+16 k, fp32 accumulation, fp16 output).  With N GPUs the problem is sharded along
+its output columns (rows of B1/B2), A replicated, no collective on the data path:
+total work is fixed, so this is strong scaling.  Rank 0 prints ONE JSON line.
+
+value      algorithmic TFLOP/s (4*M*N*K per step), inputs resident in HBM
+e2e        same metric through custom_kernel() with host buffers: pinned-host ->
+           device copies of every input and a device -> host read of C inside
+           the timed region
+roofline   tensor-core roofline of the dual-GEMM kernel
+cpu_baseline / --impl reference
+           the reference's fp32 dequantise-then-matmul CPU path (torch CPU ops,
+           all host threads) on a bounded sample of the same workload
+extra      the other benchmark configurations (skinny-M dual GEMM, G=8 grouped
+           GEMM, 64-expert MoE grouped GEMM) in microseconds per launch
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M, N, K = 8192, 14336, 4096
+WORKLOAD = "dual_gemm_swiglu_m8192_n14336_k4096"
+METRIC = "nvfp4_dual_gemm_tflops"
+UNIT = "TFLOP/s"
+L2_BYTES = 126 * 1024 * 1024
+NOMINAL_FP4_TFLOPS = 9000.0
+# CPU sample: a (rows x cols) corner of the same problem, full K
+CPU_SAMPLE = (2048, 3584, K)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        rows = []
+        for ts, line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7 and parts[0].isdigit():
+                rows.append((ts, parts))
+        inside = [p for ts, p in rows if t0 - 0.05 <= ts <= t1 + 0.15] or [p for _, p in rows]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = sorted(int(p[0]) for p in inside)
+        reasons = []
+        for idx, name in ((3, "hw_slowdown"), (4, "hw_thermal_slowdown"), (5, "sw_thermal_slowdown"),
+                          (6, "sw_power_cap")):
+            if any(p[idx].lower().startswith("active") for p in inside):
+                reasons.append(name)
+        return {"sm_mhz": int(statistics.median(busy)), "sm_max_mhz": int(inside[0][1]), "samples": len(inside),
+                "power_w_max": max((float(p[2]) for p in inside if p[2].replace(".", "", 1).isdigit()), default=None),
+                "reasons": reasons}
+
+
+# --------------------------------------------------------------------------- reference arm (CPU)
+def cpu_reference_sample(steps: int, warmup: int):
+    """The reference's CPU check (fp32 dequantise, matmul, silu*mul, fp16 cast)
+    on a corner of the benchmark problem.  Returns (TFLOP/s, seconds per step, threads)."""
+    import torch
+    pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
+    from oracle import nvfp4_oracle as orc
+    m, n, k = CPU_SAMPLE
+    data = pkg.inputs.generate_input(m, n, k, 1, 0, dist="uniform16", device="cpu")
+    for _ in range(warmup):
+        orc.dual_gemm(data)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        orc.dual_gemm(data)
+    dt = (time.perf_counter() - t0) / steps
+    flops = 4.0 * m * n * k
+    return flops / dt / 1e12, dt, torch.get_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 20))
+    tflops, dt, threads = cpu_reference_sample(steps, max(1, min(args.warmup, 3)))
+    m, n, k = CPU_SAMPLE
+    sample = f"rows 0-{m - 1} x cols 0-{n - 1} of the workload, full K={k} (4*{m}*{n}*{k} flop per step)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": max(1, min(args.warmup, 3)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32 (dequantised e2m1 x e4m3)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "l": 1,
+                   "path": "reference CPU check: fp32 dequantise-then-matmul, silu*mul, fp16 cast (torch CPU ops)"},
+        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm (GPU)
+def input_sets(pkg, torch, shard_fn, device, count, m, n, k):
+    sets = []
+    for i in range(count):
+        data = pkg.inputs.generate_input(m, n, k, 1, 42 * i, dist="uniform16", device="cpu")
+        data = shard_fn(data)
+        sets.append(data)
+    return sets
+
+
+def to_device(torch, pkg, data, device):
+    """Move the tensors custom_kernel reads (and c) to the device, keeping strides."""
+    a, b1, b2, sfa, sfb1, sfb2, sfa_p, sfb1_p, sfb2_p, c = data
+
+    def sf(t):
+        dense = t.view(torch.uint8).permute(5, 2, 4, 0, 1, 3).contiguous().to(device)
+        return dense.permute(3, 4, 1, 5, 2, 0).view(torch.float8_e4m3fn)
+
+    def fp4(t):
+        raw = t.view(torch.uint8).permute(2, 0, 1).contiguous().to(device)
+        return raw.permute(1, 2, 0).view(pkg.formats.FP4X2)
+    cc = torch.empty((1, c.shape[0], c.shape[1]), dtype=torch.float16, device=device).permute(1, 2, 0)
+    return (fp4(a), fp4(b1), fp4(b2), None, None, None, sf(sfa_p), sf(sfb1_p), sf(sfb2_p), cc)
+
+
+def time_launches(torch, fn, steps, warmup, barrier):
+    for i in range(warmup):
+        fn(i)
+    barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    start.record()
+    for i in range(steps):
+        fn(warmup + i)
+    stop.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    barrier()
+    return start.elapsed_time(stop) / 1e3, t0, t1
+
+
+def run_extra(torch, pkg, device, peaks, steps, warmup):
+    """Other benchmark configurations, one GPU: microseconds per launch."""
+    extra = {}
+    fmts = pkg.formats
+    # skinny-M dual GEMM (HBM-leaning): rotate 8 input sets (290 MB > L2)
+    m, n, k = 256, 4096, 7168
+    sets = [pkg.inputs.generate_input(m, n, k, 1, 42 * i, dist="uniform16", device=device) for i in range(8)]
+    sec, _, _ = time_launches(torch, lambda i: pkg.dual_gemm.custom_kernel(sets[i % 8]), steps * 4, warmup, lambda: None)
+    us = sec / (steps * 4) * 1e6
+    byts, flops = fmts.dual_gemm_bytes(m, n, k), fmts.dual_gemm_flops(m, n, k)
+    extra["dual_skinny_m256_n4096_k7168"] = {
+        "us_per_launch": us, "tflops": flops / us / 1e6, "hbm_gbs": byts / us / 1e3,
+        "frac_hbm_peak": byts / us / 1e3 / peaks["hbm_gbs"], "input_sets": 8}
+    del sets
+    # grouped GEMM, G=8, M_i ~ U{64..1024}, N=4096, K=7168: 2 input sets (2 x 140 MB > L2)
+    ms = pkg.inputs.uniform_group_rows(8, seed=0)
+    gsets = [pkg.inputs.generate_grouped_input(ms, [4096] * 8, [7168] * 8, 8, 42 * i, dist="uniform16", device=device)
+             for i in range(2)]
+    sec, _, _ = time_launches(torch, lambda i: pkg.group_gemm.custom_kernel(gsets[i % 2]), steps * 2, warmup, lambda: None)
+    us = sec / (steps * 2) * 1e6
+    sizes = gsets[0][3]
+    byts, flops = fmts.grouped_gemm_bytes(sizes), fmts.grouped_gemm_flops(sizes)
+    extra["grouped_g8_n4096_k7168"] = {"us_per_launch": us, "m": ms, "tflops": flops / us / 1e6,
+                                       "hbm_gbs": byts / us / 1e3, "frac_hbm_peak": byts / us / 1e3 / peaks["hbm_gbs"]}
+    del gsets
+    # MoE grouped GEMM, 64 experts, 8192 tokens top-8 (sum M = 65536), N=2048, K=7168
+    counts = pkg.inputs.moe_expert_counts(8192, 64, 8, seed=0)
+    data = pkg.inputs.generate_grouped_input(counts, [2048] * 64, [7168] * 64, 64, 0, dist="uniform16", device=device)
+    sec, _, _ = time_launches(torch, lambda i: pkg.group_gemm.custom_kernel(data), steps, warmup, lambda: None)
+    us = sec / steps * 1e6
+    byts, flops = fmts.grouped_gemm_bytes(data[3]), fmts.grouped_gemm_flops(data[3])
+    extra["grouped_moe_g64_n2048_k7168"] = {
+        "us_per_launch": us, "m_min": min(counts), "m_max": max(counts), "zero_groups": counts.count(0),
+        "tflops": flops / us / 1e6, "frac_fp4_nominal": flops / us / 1e6 / NOMINAL_FP4_TFLOPS,
+        "hbm_gbs": byts / us / 1e3}
+    return extra
+
+
+def run_ours(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the NVFP4 kernels have no CPU path")
+    torch.cuda.set_device(local)
+    device = f"cuda:{local}"
+    pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
+    pkg._lib.load()
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(device))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    peaks = load_peaks()
+    lo, hi = pkg.shard.column_range(N, rank, world)
+    n_local = hi - lo
+    shard = (lambda d: pkg.shard.shard_dual_input(d, rank, world))
+    # rotate enough input sets that their bytes exceed 2 x L2
+    per_set = M * K // 2 + 2 * (n_local * K // 2)
+    n_sets = max(2, min(8, -(-2 * L2_BYTES // per_set)))
+    host_sets = input_sets(pkg, torch, shard, device, n_sets, M, N, K)
+    dev_sets = [to_device(torch, pkg, d, device) for d in host_sets]
+
+    launches0 = pkg._lib.launch_count()
+    sampler = ClockSampler(local)
+    sampler.start()
+    sec, t0, t1 = time_launches(torch, lambda i: pkg.dual_gemm.custom_kernel(dev_sets[i % n_sets]), args.steps,
+                                args.warmup, barrier)
+    clocks = sampler.stop(t0, t1)
+    launches = pkg._lib.launch_count() - launches0 - args.warmup
+    status = pkg._lib.read_status(local)
+    if status:
+        raise SystemExit(f"device status word {status:#x}: an on-device wait timed out")
+    t = torch.tensor([sec], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    sec_max = float(t.item())
+    flops_total = 4.0 * M * N * K
+    value = flops_total * args.steps / sec_max / 1e12
+
+    # ---- end to end: pinned host buffers -> device, kernel, C back to the host
+    hs = host_sets[0]
+
+    def pin_bytes(t_):
+        return t_.view(torch.uint8).permute(2, 0, 1).contiguous().pin_memory()
+
+    def pin_sf(t_):
+        return t_.view(torch.uint8).permute(5, 2, 4, 0, 1, 3).contiguous().pin_memory()
+    h_ops = [pin_bytes(x) for x in hs[:3]]
+    h_sfs = [pin_sf(x) for x in hs[6:9]]
+    d_ops = [torch.empty_like(x, device=device) for x in h_ops]
+    d_sfs = [torch.empty_like(x, device=device) for x in h_sfs]
+    d_c = torch.empty((1, M, n_local), dtype=torch.float16, device=device)
+    h_c = torch.empty((1, M, n_local), dtype=torch.float16).pin_memory()
+    d_data = tuple(x.permute(1, 2, 0).view(pkg.formats.FP4X2) for x in d_ops) + (None, None, None) + \
+        tuple(x.permute(3, 4, 1, 5, 2, 0).view(torch.float8_e4m3fn) for x in d_sfs) + (d_c.permute(1, 2, 0),)
+    h2d = sum(x.numel() for x in h_ops + h_sfs)
+    d2h = h_c.numel() * 2
+
+    def e2e_step(_i):
+        for src, dst in zip(h_ops + h_sfs, d_ops + d_sfs):
+            dst.copy_(src, non_blocking=True)
+        pkg.dual_gemm.custom_kernel(d_data)
+        h_c.copy_(d_c, non_blocking=True)
+    e2e_steps = max(2, min(args.steps, 10))
+    sec_e2e, _, _ = time_launches(torch, e2e_step, e2e_steps, 1, barrier)
+    t = torch.tensor([sec_e2e], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = flops_total * e2e_steps / float(t.item()) / 1e12
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    fp4_peak = 4.0 * peaks["bf16_tflops"]
+    per_launch_flops = 4.0 * M * n_local * K
+    achieved = per_launch_flops * args.steps / sec / 1e12     # this rank's kernel
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
+        "peak_basis": f"4 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no measured FP4 "
+                      f"figure exists; nominal dense NVFP4 is {NOMINAL_FP4_TFLOPS:.0f}",
+        "frac_nominal": achieved / NOMINAL_FP4_TFLOPS, "kernel": "nvfp4_gemm_persistent<Dual>",
+        "avg_launch_us": sec / args.steps * 1e6, "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
+        "algorithmic_bytes": pkg.formats.dual_gemm_bytes(M, n_local, K),
+    }
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec_max / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scale), f32 accumulate, f16 out",
+        "data": "synthetic", "gpu_launches": int(launches),
+        "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "l": 1, "n_per_gpu": n_local,
+                   "parallelism": f"column-sharded x{world}, A replicated, no collective",
+                   "operands": "e2m1 codes uniform over 16 values, e4m3 scales U[0.25,2], seeds 0,42,..",
+                   "l2": f"rotating {n_sets} input sets ({n_sets * per_set / 1e6:.0f} MB > L2 126 MB) plus "
+                         f"{2 * M * n_local / 1e6:.0f} MB of C written per step"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "steps": e2e_steps},
+        "clocks": clocks, "roofline": roofline,
+    }
+    if world == 1:
+        cpu_tflops, cpu_dt, threads = cpu_reference_sample(3, 1)
+        m_, n_, k_ = CPU_SAMPLE
+        line["cpu_baseline"] = {"value": cpu_tflops, "unit": UNIT, "cores": threads, "kind": "port",
+                                "sample": f"{m_}x{n_} corner of the workload, full K={k_}, 3 timed passes "
+                                          f"({cpu_dt:.2f} s each)"}
+        if not args.no_extra:
+            del dev_sets, host_sets
+            torch.cuda.empty_cache()
+            line["extra"] = run_extra(torch, pkg, device, peaks, max(5, args.steps), max(3, args.warmup))
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one full-size dual-GEMM launch, from the ncu capture
+# summarised in profiles/; None until measured.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
