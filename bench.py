@@ -278,6 +278,16 @@ def run_ours(args):
     flops_total = 4.0 * M * N * K
     value = flops_total * args.steps / sec_max / 1e12
 
+    if args.kernel_only:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": sec_max / args.steps * 1e3,
+                              "config": {"workload": WORKLOAD}, "gpu_launches": int(launches), "clocks": clocks,
+                              "note": "kernel-only run for profiler captures"}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
     # ---- end to end: pinned host buffers -> device, kernel, C back to the host
     hs = host_sets[0]
 
@@ -362,11 +372,18 @@ TRAFFIC_BYTES_PER_LAUNCH = None
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="only the device-timed launches (no e2e, CPU baseline or extras): for profiler captures")
+    ap.add_argument("--shape", default=None, help="M,N,K override of the dual-GEMM shape (profiler captures)")
     args = ap.parse_args()
+    if args.shape:
+        global M, N, K, WORKLOAD
+        M, N, K = (int(x) for x in args.shape.split(","))
+        WORKLOAD = f"dual_gemm_m{M}_n{N}_k{K}"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -38,6 +38,12 @@ extern "C" {
 #define B200_VARIANT_SPLITK 4     /* persistent kernel, k-range split over CTAs with an
                                      fp32 partial-sum exchange before the epilogue     */
 
+/* Dual GEMM only: variant = B200_VARIANT_PROBE_BASE + bits runs the persistent
+ * kernel with parts of its data path switched off (bit 1: scale-factor copies,
+ * 2: MMAs, 3: second B tile, 4: stores, 5: all loads; bit 0: two N=128 MMAs).
+ * For timing experiments; the output is undefined. */
+#define B200_VARIANT_PROBE_BASE 100
+
 /* Library version string, e.g. "b200nvfp4 0.1 (sm_100a)". */
 const char* b200_version(void);
 

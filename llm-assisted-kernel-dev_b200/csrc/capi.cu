@@ -118,6 +118,8 @@ int device_state(int device, DeviceState** out) {
         B200_CUDA(cudaMemset(st.status, 0, sizeof(uint32_t)));
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Dual, kDualStages>,
                               smem_bytes_persistent<Mode::Dual, kDualStages>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Dual, kDualStages, true>,
+                              smem_bytes_persistent<Mode::Dual, kDualStages>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Group128, kG128Stages>,
                               smem_bytes_persistent<Mode::Group128, kG128Stages>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Group256, kG256Stages>,
@@ -183,10 +185,11 @@ int validate_dual(const void* a, const void* b1, const void* b2, const void* sfa
     return 0;
 }
 
-template <Mode M, int kStages, typename P>
-int launch_persistent(const P& prob, int units, int sm_count, int two_mma, cudaStream_t stream) {
+template <Mode M, int kStages, typename P, bool kTimingProbes = false>
+int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStream_t stream) {
     const int grid = units < sm_count ? units : sm_count;
-    nvfp4_gemm_persistent<M, kStages><<<grid, 192, smem_bytes_persistent<M, kStages>(), stream>>>(prob, two_mma);
+    nvfp4_gemm_persistent<M, kStages, kTimingProbes>
+        <<<grid, kPersistentThreads, smem_bytes_persistent<M, kStages>(), stream>>>(prob, flags);
     B200_CUDA(cudaGetLastError());
     ++g_launches;
     return 0;
@@ -229,7 +232,8 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     if (sfb_batch_bytes == 0) sfb_batch_bytes = static_cast<int64_t>(n / 128) * (k / 64) * 512;
     int rc = validate_dual(a, b1, b2, sfa, sfb1, sfb2, c, m, n, k, l, ldc, c_batch, b_batch_bytes, sfb_batch_bytes);
     if (rc) return rc;
-    if (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_SPLITK)
+    const bool probe = variant >= B200_VARIANT_PROBE_BASE && variant < B200_VARIANT_PROBE_BASE + 64;
+    if (!probe && (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_SPLITK))
         return fail(B200_E_VARIANT, "dual gemm: unknown variant %d", variant);
     if (variant == B200_VARIANT_SPLITK) return fail(B200_E_VARIANT, "dual gemm: split-k variant not built");
 
@@ -277,6 +281,9 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     p.status = status ? status : st->status;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (probe)
+        return launch_persistent<Mode::Dual, kDualStages, DenseProblem, true>(p, p.total_tiles, st->sm_count,
+                                                                              variant - B200_VARIANT_PROBE_BASE, s);
     switch (variant) {
         case B200_VARIANT_SERIAL:
             return launch_serial<Mode::Dual>(p, p.total_tiles, 0, s);

@@ -35,8 +35,20 @@ constexpr uint32_t kStatusMmaWaitAcc = 0x4;
 constexpr uint32_t kStatusEpilogueWait = 0x8;
 constexpr uint32_t kStatusSerialWait = 0x10;
 constexpr uint32_t kStatusSplitKWait = 0x20;
+constexpr uint32_t kStatusSfWait = 0x40;
 
 enum class Mode { Dual, Group128, Group256 };
+
+// Bits of the kernels' `flags` argument.  Bit 0 selects two N=128 MMAs per
+// k-block instead of one N=256 MMA.  The others switch parts of the data path
+// off for timing experiments (results are then wrong by design); they are only
+// honoured by kernels instantiated with kTimingProbes = true.
+constexpr int kFlagTwoMma = 1;
+constexpr int kFlagSkipSfCopy = 2;     // scale factors copied to TMEM only for a tile's first k-tile
+constexpr int kFlagSkipMma = 4;        // only the first k-block of every k-tile is multiplied
+constexpr int kFlagSkipBHi = 8;        // second B tile (and its scale factors) not loaded
+constexpr int kFlagSkipStores = 16;    // epilogue drains TMEM but stores nothing
+constexpr int kFlagSkipLoads = 32;     // producer signals stages full without loading anything
 
 template <Mode M> struct ModeTraits;
 template <> struct ModeTraits<Mode::Dual> {
@@ -216,19 +228,32 @@ template <Mode M> struct StageLayout {
     static constexpr uint32_t kTxBytes = kBytes;
 };
 
-// TMEM columns.  N=256 accumulators: two buffers at columns 0 and 208 that share
-// columns [208,256); scale factors in the last 48 columns.  The epilogue drains
-// the shared columns first and hands them back before it does anything else, so
-// the next tile's MMAs overlap with the rest of the epilogue.
+// TMEM columns (512 per SM).
+// N=256 accumulators: two buffers at columns 0 and 160 that share columns
+// [160,256); the epilogue first pulls the shared columns into registers and
+// hands them back, so the next tile's MMAs overlap with the rest of the epilogue.
 // N=128 accumulators: two disjoint buffers at 0 and 128.
+// Scale factors: a ring of eight slots, one per 64-k block (SFA 4 columns + SFB
+// kMmaN/32 columns), handed over slot by slot.  In the persistent kernel they
+// are written by four dedicated warps with tcgen05.st (shared memory ->
+// registers -> TMEM, one warp per 32-lane quadrant, which gives the 4x
+// replication the MMA expects for free).  A tcgen05.cp costs the tensor pipe
+// 30-60 cycles whatever its size, and NVFP4 needs twelve of them per four MMAs,
+// so copying through the tensor pipe caps it near half of its peak; the serial
+// bring-up kernel still uses tcgen05.cp.
 template <Mode M> struct TmemMap {
     using T = ModeTraits<M>;
     static constexpr bool kOverlapped = (T::kMmaN == 256);
-    static constexpr uint32_t kAccStride = kOverlapped ? 208 : 128;
-    static constexpr uint32_t kSfA = kOverlapped ? 464 : 256;         // 4 columns per k-block
-    static constexpr uint32_t kSfB = kSfA + 16;                        // kMmaN/32 columns per k-block
-    static constexpr uint32_t kSfBPerBlock = T::kMmaN / 32;
-    static constexpr int kEarlyChunks = kOverlapped ? 3 : 0;          // 48 shared columns / 16
+    static constexpr uint32_t kAccStride = kOverlapped ? 160 : 128;
+    static constexpr uint32_t kSharedBegin = 160;                      // columns shared by the two buffers
+    static constexpr uint32_t kSfBase = kOverlapped ? 416 : 256;
+    static constexpr uint32_t kSfBCols = T::kMmaN / 32;
+    static constexpr uint32_t kSlotCols = 4 + kSfBCols;
+    static constexpr int kSlots = 8;
+    static constexpr int kEarlyChunks = kOverlapped ? 6 : 0;          // 96 shared columns / 16
+    static_assert(kSfBase + kSlots * kSlotCols <= kTmemColumns, "TMEM budget");
+    __device__ static constexpr uint32_t sfa_col(int slot) { return kSfBase + slot * kSlotCols; }
+    __device__ static constexpr uint32_t sfb_col(int slot) { return kSfBase + slot * kSlotCols + 4; }
 };
 
 struct ControlBlock {
@@ -236,6 +261,8 @@ struct ControlBlock {
     uint64_t empty[8];
     uint64_t acc_full[2];
     uint64_t acc_release[2];
+    uint64_t sf_ready[8];     // scale factors of one 64-k block are in TMEM slot i
+    uint64_t sf_free[8];      // the MMA that read TMEM slot i has retired
     uint64_t aux;
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
@@ -248,57 +275,62 @@ template <Mode M, int kStages> constexpr uint32_t smem_bytes_persistent() {
 // ---------------------------------------------------------------------------
 // Role bodies shared by the persistent and the serial kernel
 // ---------------------------------------------------------------------------
-template <Mode M>
-__device__ __forceinline__ void issue_stage_loads(const Work& w, int kt, uint32_t stage, uint32_t bar) {
+template <Mode M, bool kTimingProbes = false>
+__device__ __forceinline__ void issue_stage_loads(const Work& w, int kt, uint32_t stage, uint32_t bar,
+                                                  int flags = 0) {
     using L = StageLayout<M>;
-    mbar_arrive_expect_tx(bar, L::kTxBytes);
+    bool load_hi = ModeTraits<M>::kHasBHi;
+    if constexpr (kTimingProbes) {
+        if (flags & kFlagSkipLoads) {
+            mbar_arrive(bar);
+            return;
+        }
+        if (flags & kFlagSkipBHi) load_hi = false;
+    }
+    mbar_arrive_expect_tx(bar, load_hi || !ModeTraits<M>::kHasBHi ? L::kTxBytes
+                                                                   : L::kTxBytes - kOperandTileBytes - kSfChunkBytes);
     const int kbyte = kt * 128;
     tma_load_3d(stage + L::kOffA, w.map_a, bar, kbyte, w.a_row, w.batch);
     tma_load_3d(stage + L::kOffBLo, w.map_blo, bar, kbyte, w.blo_row, w.batch);
-    if constexpr (ModeTraits<M>::kHasBHi)
-        tma_load_3d(stage + L::kOffBHi, w.map_bhi, bar, kbyte, w.bhi_row, w.batch);
+    if (load_hi) tma_load_3d(stage + L::kOffBHi, w.map_bhi, bar, kbyte, w.bhi_row, w.batch);
     const long long sf_off = static_cast<long long>(kt) * kSfChunkBytes;
     bulk_load(stage + L::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
     bulk_load(stage + L::kOffSfBLo, w.sfblo + sf_off, kSfChunkBytes, bar);
-    if constexpr (ModeTraits<M>::kHasBHi)
-        bulk_load(stage + L::kOffSfBHi, w.sfbhi + sf_off, kSfChunkBytes, bar);
+    if (load_hi) bulk_load(stage + L::kOffSfBHi, w.sfbhi + sf_off, kSfChunkBytes, bar);
 }
 
-// Scale factors smem -> TMEM, then the four 64-k MMAs of one k-tile.
-// `two_mma`: issue two N=128 MMAs (B-lo, B-hi) instead of one N=256 MMA.
+// Scale factors of k-block `kb` of the k-tile in `stage`: shared memory -> TMEM slot.
 template <Mode M>
-__device__ __forceinline__ void issue_stage_mma(uint32_t stage, uint32_t tmem_base, uint32_t acc_col,
-                                                bool first_k_tile, bool two_mma) {
+__device__ __forceinline__ void issue_sf_copy(uint32_t stage, uint32_t tmem_base, int kb, int slot) {
+    using L = StageLayout<M>;
+    using TM = TmemMap<M>;
+    tc_cp_32x128b_warpx4(tmem_base + TM::sfa_col(slot), smem_desc_sf(stage + L::kOffSfA + kb * kSfAtomBytes));
+    tc_cp_32x128b_warpx4(tmem_base + TM::sfb_col(slot), smem_desc_sf(stage + L::kOffSfBLo + kb * kSfAtomBytes));
+    if constexpr (ModeTraits<M>::kHasBHi)
+        tc_cp_32x128b_warpx4(tmem_base + TM::sfb_col(slot) + 4,
+                             smem_desc_sf(stage + L::kOffSfBHi + kb * kSfAtomBytes));
+}
+
+// The MMA of k-block `kb` (64 e2m1 elements = 32 bytes along k: +2 in the
+// descriptor's address field inside the 128-byte swizzle atom).
+// `two_mma`: two N=128 MMAs (B-lo, B-hi) instead of one N=256 MMA.
+template <Mode M>
+__device__ __forceinline__ void issue_mma(uint32_t stage, uint32_t tmem_base, uint32_t acc_col, int kb, int slot,
+                                          uint32_t accumulate, bool two_mma) {
     using L = StageLayout<M>;
     using T = ModeTraits<M>;
     using TM = TmemMap<M>;
-#pragma unroll
-    for (int kb = 0; kb < kKBlocks; ++kb) {
-        tc_cp_32x128b_warpx4(tmem_base + TM::kSfA + 4 * kb, smem_desc_sf(stage + L::kOffSfA + kb * kSfAtomBytes));
-        tc_cp_32x128b_warpx4(tmem_base + TM::kSfB + TM::kSfBPerBlock * kb,
-                             smem_desc_sf(stage + L::kOffSfBLo + kb * kSfAtomBytes));
-        if constexpr (T::kHasBHi)
-            tc_cp_32x128b_warpx4(tmem_base + TM::kSfB + TM::kSfBPerBlock * kb + 4,
-                                 smem_desc_sf(stage + L::kOffSfBHi + kb * kSfAtomBytes));
-    }
-    const uint64_t adesc = smem_desc_sw128(stage + L::kOffA);
-    const uint64_t bdesc = smem_desc_sw128(stage + L::kOffBLo);
-#pragma unroll
-    for (int kb = 0; kb < kKBlocks; ++kb) {
-        const uint32_t acc = (first_k_tile && kb == 0) ? 0u : 1u;
-        const uint32_t sfa = tmem_base + TM::kSfA + 4 * kb;
-        const uint32_t sfb = tmem_base + TM::kSfB + TM::kSfBPerBlock * kb;
-        // +32 bytes along k inside the 128-byte swizzle atom = +2 in the address field
-        if (T::kHasBHi && two_mma) {
-            const uint64_t bdesc_hi = smem_desc_sw128(stage + L::kOffBHi);
-            tc_mma_mxf4nvf4(tmem_base + acc_col, adesc + 2 * kb, bdesc + 2 * kb, idesc_mxf4nvf4(128, 128), sfa,
-                            sfb, acc);
-            tc_mma_mxf4nvf4(tmem_base + acc_col + 128, adesc + 2 * kb, bdesc_hi + 2 * kb,
-                            idesc_mxf4nvf4(128, 128), sfa, sfb + 4, acc);
-        } else {
-            tc_mma_mxf4nvf4(tmem_base + acc_col, adesc + 2 * kb, bdesc + 2 * kb,
-                            idesc_mxf4nvf4(128, T::kMmaN), sfa, sfb, acc);
-        }
+    const uint64_t adesc = smem_desc_sw128(stage + L::kOffA) + 2 * kb;
+    const uint64_t bdesc = smem_desc_sw128(stage + L::kOffBLo) + 2 * kb;
+    const uint32_t sfa = tmem_base + TM::sfa_col(slot);
+    const uint32_t sfb = tmem_base + TM::sfb_col(slot);
+    if (T::kHasBHi && two_mma) {
+        const uint64_t bdesc_hi = smem_desc_sw128(stage + L::kOffBHi) + 2 * kb;
+        tc_mma_mxf4nvf4(tmem_base + acc_col, adesc, bdesc, idesc_mxf4nvf4(128, 128), sfa, sfb, accumulate);
+        tc_mma_mxf4nvf4(tmem_base + acc_col + 128, adesc, bdesc_hi, idesc_mxf4nvf4(128, 128), sfa, sfb + 4,
+                        accumulate);
+    } else {
+        tc_mma_mxf4nvf4(tmem_base + acc_col, adesc, bdesc, idesc_mxf4nvf4(128, T::kMmaN), sfa, sfb, accumulate);
     }
 }
 
@@ -322,59 +354,71 @@ __device__ __forceinline__ void store_chunk(__half* row_ptr, int chunk, const ui
 }
 
 // Epilogue of one tile for one warp (TMEM lane quadrant `quad`).  When the
-// accumulator buffers overlap, the chunks living in the shared columns are
-// pulled into registers first and `release` is signalled before any math.
+// accumulator buffers overlap, the 96 shared columns are pulled into registers
+// first and `release` is signalled before any math; their partner columns (the
+// other product of the dual GEMM) are not shared and are read later.
+//   buffer 0 (columns 0-255):   shared = its columns 160-255
+//   buffer 1 (columns 160-415): shared = its columns 0-95
 template <Mode M, int kBuf>
 __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base, int quad, int lane,
-                                              uint32_t release_bar) {
+                                              uint32_t release_bar, bool store = true) {
     using T = ModeTraits<M>;
     using TM = TmemMap<M>;
     constexpr int kChunks = T::kOutCols / 16;
     constexpr int kEarly = TM::kEarlyChunks;
-    constexpr int kEarlyBegin = (kBuf == 0) ? kChunks - kEarly : 0;
+    constexpr int kSharedRel = (kBuf == 0) ? TM::kSharedBegin : 0;    // first shared column, buffer-relative
     const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
     const int row = quad * 32 + lane;
-    const bool row_ok = row < w.rows_valid;
+    const bool row_ok = store && row < w.rows_valid;
     __half* row_ptr = w.c + static_cast<long long>(row) * w.ldc;
 
+    uint32_t early[kEarly > 0 ? kEarly : 1][16];
     if constexpr (kEarly > 0) {
-        uint32_t ex[kEarly][16], ey[kEarly][16];
 #pragma unroll
-        for (int i = 0; i < kEarly; ++i) {
-            tc_ld_x16(acc + (kEarlyBegin + i) * 16, ex[i]);
-            if constexpr (T::kSilu) tc_ld_x16(acc + 128 + (kEarlyBegin + i) * 16, ey[i]);
-        }
+        for (int i = 0; i < kEarly; ++i) tc_ld_x16(acc + kSharedRel + i * 16, early[i]);
         tc_wait_ld();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(release_bar);
-#pragma unroll
-        for (int i = 0; i < kEarly; ++i) {
-            const int chunk = kEarlyBegin + i;
-            if (row_ok && chunk * 16 < w.cols_valid) store_chunk<T::kSilu>(row_ptr, chunk, ex[i], T::kSilu ? ey[i] : ex[i]);
-        }
     }
+    // Which buffer-relative 16-column group feeds x (and y) of output chunk c,
+    // and whether that group sits in `early`.
 #pragma unroll
     for (int chunk = 0; chunk < kChunks; ++chunk) {
-        if (kEarly > 0 && chunk >= kEarlyBegin && chunk < kEarlyBegin + kEarly) continue;
+        constexpr int kYBase = 128;                      // dual: second product starts at column 128
+        const int xcol = chunk * 16;
+        const int ycol = kYBase + chunk * 16;
+        const bool x_early = kEarly > 0 && xcol >= kSharedRel && xcol < kSharedRel + kEarly * 16;
+        const bool y_early = T::kSilu && kEarly > 0 && ycol >= kSharedRel && ycol < kSharedRel + kEarly * 16;
         uint32_t x[16], y[16];
-        tc_ld_x16(acc + chunk * 16, x);
-        if constexpr (T::kSilu) tc_ld_x16(acc + 128 + chunk * 16, y);
-        tc_wait_ld();
+        if (!x_early) tc_ld_x16(acc + xcol, x);
+        if (T::kSilu && !y_early) tc_ld_x16(acc + ycol, y);
+        if (!x_early || (T::kSilu && !y_early)) tc_wait_ld();
+        if (x_early) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = early[(xcol - kSharedRel) / 16][i];
+        }
+        if (y_early) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y[i] = early[(ycol - kSharedRel) / 16][i];
+        }
         if (row_ok && chunk * 16 < w.cols_valid) store_chunk<T::kSilu>(row_ptr, chunk, x, T::kSilu ? y : x);
     }
 }
 
 // ---------------------------------------------------------------------------
-// Persistent warp-specialised kernel: 6 warps.
+// Persistent warp-specialised kernel: 10 warps.
 //   warps 0-3  epilogue (TMEM lane quadrants 0-3)
 //   warp 4     TMEM allocation + MMA issue (one lane)
 //   warp 5     TMA producer (one lane)
+//   warps 6-9  scale factors shared memory -> TMEM (quadrants 2, 3, 0, 1)
 // CTA b walks work units b, b+grid, b+2*grid, ...
 // ---------------------------------------------------------------------------
-template <Mode M, int kStages>
-__global__ void __launch_bounds__(192, 1)
-nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, int two_mma) {
+constexpr int kPersistentThreads = 320;
+
+template <Mode M, int kStages, bool kTimingProbes = false>
+__global__ void __launch_bounds__(kPersistentThreads, 1)
+nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, int flags) {
     using L = StageLayout<M>;
     using TM = TmemMap<M>;
     using S = Scheduler<M>;
@@ -394,6 +438,10 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
             mbar_init(smem_u32(&ctl->acc_full[b]), 1);
             mbar_init(smem_u32(&ctl->acc_release[b]), 4);
         }
+        for (int i = 0; i < TM::kSlots; ++i) {
+            mbar_init(smem_u32(&ctl->sf_ready[i]), 4);
+            mbar_init(smem_u32(&ctl->sf_free[i]), 1);
+        }
         mbar_init(smem_u32(&ctl->aux), 1);
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -410,7 +458,66 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
     const int total = S::total_units(p);
     volatile uint32_t* abort_flag = &ctl->abort_flag;
 
-    if (warp == 5) {
+    if (warp >= 6) {
+        // ------------------------------ scale factors: shared memory -> TMEM
+        // Lane r of the warp serving quadrant q reads row r of each 512-byte atom
+        // (16 bytes = the row's scale factors for four 16-k blocks of four 32-row
+        // groups) and writes it to TMEM lane 32q + r, four columns per atom.  A
+        // whole k-tile is read into registers as soon as its stage lands; each
+        // 64-k block is then written the moment its ring slot is free.
+        const uint32_t quad_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        uint32_t s = 0, ph = 0, g = 0;     // stage, its phase, running 64-k block count
+        int cursor = 0;
+        bool ok = true;
+        const bool skip = kTimingProbes && (flags & kFlagSkipSfCopy);
+        constexpr int kAtoms = ModeTraits<M>::kHasBHi ? 3 : 2;
+        for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x) {
+            const Work w = S::get(p, unit, cursor);
+            for (int i = 0; ok && i < w.k_tile_count; ++i) {
+                if (!mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusSfWait)) {
+                    ok = false;
+                    break;
+                }
+                uint32_t v[kKBlocks][kAtoms][4];
+                const uint32_t src = smem_base + s * L::kBytes + lane * 16;
+#pragma unroll
+                for (int kb = 0; kb < kKBlocks; ++kb) {
+                    ld_shared_v4(src + L::kOffSfA + kb * kSfAtomBytes, v[kb][0][0], v[kb][0][1], v[kb][0][2], v[kb][0][3]);
+                    ld_shared_v4(src + L::kOffSfBLo + kb * kSfAtomBytes, v[kb][1][0], v[kb][1][1], v[kb][1][2],
+                                 v[kb][1][3]);
+                    if constexpr (kAtoms == 3)
+                        ld_shared_v4(src + L::kOffSfBHi + kb * kSfAtomBytes, v[kb][2][0], v[kb][2][1], v[kb][2][2],
+                                     v[kb][2][3]);
+                }
+#pragma unroll
+                for (int kb = 0; kb < kKBlocks; ++kb, ++g) {
+                    const int slot = g & (TM::kSlots - 1);
+                    if (g >= static_cast<uint32_t>(TM::kSlots)) {
+                        if (!mbar_wait(smem_u32(&ctl->sf_free[slot]), ((g >> 3) - 1u) & 1u, abort_flag, p.status,
+                                       kStatusSfWait)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                    }
+                    if (!skip || g < static_cast<uint32_t>(TM::kSlots)) {
+                        tc_st_x4(tmem_base + quad_lane + TM::sfa_col(slot), v[kb][0][0], v[kb][0][1], v[kb][0][2],
+                                 v[kb][0][3]);
+                        tc_st_x4(tmem_base + quad_lane + TM::sfb_col(slot), v[kb][1][0], v[kb][1][1], v[kb][1][2],
+                                 v[kb][1][3]);
+                        if constexpr (kAtoms == 3)
+                            tc_st_x4(tmem_base + quad_lane + TM::sfb_col(slot) + 4, v[kb][2][0], v[kb][2][1],
+                                     v[kb][2][2], v[kb][2][3]);
+                        tc_wait_st();
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_ready[slot]));
+                }
+                if (++s == kStages) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 5) {
         // ------------------------------ TMA producer
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
@@ -428,7 +535,8 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                         ok = false;
                         break;
                     }
-                    issue_stage_loads<M>(w, w.k_tile_begin + i, smem_base + s * L::kBytes, smem_u32(&ctl->full[s]));
+                    issue_stage_loads<M, kTimingProbes>(w, w.k_tile_begin + i, smem_base + s * L::kBytes,
+                                                        smem_u32(&ctl->full[s]), flags);
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -441,14 +549,16 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
     } else if (warp == 4) {
         // ------------------------------ MMA issuer
         if (lane == 0) {
-            uint32_t s = 0, ph = 0;
+            uint32_t s = 0, ph = 0, g = 0;   // stage, its phase, running 64-k block count
             int cursor = 0, it = 0;
+            const bool two_mma = (flags & kFlagTwoMma) != 0;
+            const int mma_blocks = (kTimingProbes && (flags & kFlagSkipMma)) ? 1 : kKBlocks;
             bool ok = true;
             for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x, ++it) {
                 const Work w = S::get(p, unit, cursor);
                 if (it > 0) {
-                    const int j = it - 1;   // wait for hand-back number j
-                    if (!mbar_wait(smem_u32(&ctl->acc_release[j & 1]), (j >> 1) & 1, abort_flag, p.status,
+                    const int r = it - 1;   // wait for hand-back number r
+                    if (!mbar_wait(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
                                    kStatusMmaWaitAcc)) {
                         ok = false;
                         break;
@@ -456,14 +566,26 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                     tc_fence_after_sync();
                 }
                 const uint32_t acc_col = (it & 1) * TM::kAccStride;
-                for (int i = 0; i < w.k_tile_count; ++i) {
+                for (int i = 0; ok && i < w.k_tile_count; ++i) {
                     if (!mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusMmaWaitFull)) {
                         ok = false;
                         break;
                     }
-                    tc_fence_after_sync();
-                    issue_stage_mma<M>(smem_base + s * L::kBytes, tmem_base, acc_col, i == 0, two_mma != 0);
-                    tc_commit(smem_u32(&ctl->empty[s]));   // frees the stage once these MMAs retire
+                    const uint32_t stage = smem_base + s * L::kBytes;
+#pragma unroll
+                    for (int kb = 0; kb < kKBlocks; ++kb, ++g) {
+                        const int slot = g & (TM::kSlots - 1);
+                        if (!mbar_wait(smem_u32(&ctl->sf_ready[slot]), (g >> 3) & 1u, abort_flag, p.status,
+                                       kStatusMmaWaitFull)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        if (kb < mma_blocks)
+                            issue_mma<M>(stage, tmem_base, acc_col, kb, slot, (i > 0 || kb > 0) ? 1u : 0u, two_mma);
+                        tc_commit(smem_u32(&ctl->sf_free[slot]));   // slot reusable once this MMA retires
+                    }
+                    tc_commit(smem_u32(&ctl->empty[s]));            // stage reusable once these MMAs retire
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) tc_commit(smem_u32(&ctl->acc_full[it & 1]));
@@ -491,10 +613,11 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                 break;
             }
             tc_fence_after_sync();
+            const bool store = !(kTimingProbes && (flags & kFlagSkipStores));
             if (it & 1)
-                epilogue_tile<M, 1>(w, tmem_base, warp, lane, release_bar);
+                epilogue_tile<M, 1>(w, tmem_base, warp, lane, release_bar, store);
             else
-                epilogue_tile<M, 0>(w, tmem_base, warp, lane, release_bar);
+                epilogue_tile<M, 0>(w, tmem_base, warp, lane, release_bar, store);
             tc_fence_before_sync();
         }
     }
@@ -513,7 +636,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
 // ---------------------------------------------------------------------------
 template <Mode M>
 __global__ void __launch_bounds__(128, 1)
-nvfp4_gemm_serial(const __grid_constant__ typename Scheduler<M>::Params p, int two_mma) {
+nvfp4_gemm_serial(const __grid_constant__ typename Scheduler<M>::Params p, int flags) {
     using L = StageLayout<M>;
     using S = Scheduler<M>;
     extern __shared__ uint8_t smem_raw[];
@@ -552,7 +675,12 @@ nvfp4_gemm_serial(const __grid_constant__ typename Scheduler<M>::Params p, int t
                 issue_stage_loads<M>(w, w.k_tile_begin + i, smem_base, smem_u32(&ctl->full[0]));
                 if (!mbar_wait(smem_u32(&ctl->full[0]), ph, abort_flag, p.status, kStatusSerialWait)) break;
                 tc_fence_after_sync();
-                issue_stage_mma<M>(smem_base, tmem_base, 0, i == 0, two_mma != 0);
+#pragma unroll
+                for (int kb = 0; kb < kKBlocks; ++kb) issue_sf_copy<M>(smem_base, tmem_base, kb, kb);
+#pragma unroll
+                for (int kb = 0; kb < kKBlocks; ++kb)
+                    issue_mma<M>(smem_base, tmem_base, 0, kb, kb, (i > 0 || kb > 0) ? 1u : 0u,
+                                 (flags & kFlagTwoMma) != 0);
                 tc_commit(smem_u32(&ctl->empty[0]));
                 if (!mbar_wait(smem_u32(&ctl->empty[0]), ph, abort_flag, p.status, kStatusSerialWait)) break;
             }

@@ -79,23 +79,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait: gives up after `timeout_ns`, ORs `code` into *status, raises the
-// CTA-wide abort flag and returns false.  Never traps, never spins forever.
-constexpr uint64_t kWaitTimeoutNs = 1000ull * 1000ull * 1000ull;  // 1 s
+// Bounded wait: gives up after about a second (kWaitTimeoutCycles SM clocks),
+// ORs `code` into *status, raises the CTA-wide abort flag and returns false.
+// Never traps, never spins forever.  The deadline is kept with clock64(), which
+// costs a few cycles; %globaltimer is far slower to read and would sit on the
+// wake-up path of every wait that does not succeed at once.
+constexpr long long kWaitTimeoutCycles = 2000ll * 1000ll * 1000ll;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t code) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
 #pragma unroll 1
     while (true) {
 #pragma unroll 1
-        for (int i = 0; i < 128; ++i)
+        for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > kWaitTimeoutNs) {
+        if (clock64() - t0 > kWaitTimeoutCycles) {
             *abort_flag = 1u;
             atomicOr(status, code);
             return false;
@@ -234,6 +235,20 @@ __device__ __forceinline__ void tc_ld_x16(uint32_t taddr, uint32_t (&v)[16]) {
           "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
+}
+// Registers -> TMEM: lane i of the warp writes 4 consecutive 32-bit columns of
+// TMEM lane (taddr.lane + i).  The warp may only touch its own lane quadrant.
+__device__ __forceinline__ void tc_st_x4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b),
+                 "r"(c), "r"(d)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr)
+                 : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
