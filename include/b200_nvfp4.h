@@ -39,9 +39,11 @@ extern "C" {
                                      fp32 partial-sum exchange before the epilogue     */
 
 /* Dual GEMM only: variant = B200_VARIANT_PROBE_BASE + bits runs the persistent
- * kernel with parts of its data path switched off (bit 1: scale-factor copies,
- * 2: MMAs, 3: second B tile, 4: stores, 5: all loads; bit 0: two N=128 MMAs).
- * For timing experiments; the output is undefined. */
+ * kernel with parts of its data path switched off (bit 1: scale-factor stores,
+ * 2: three of four MMAs, 3: second B tile, 4: global stores, 5: all loads,
+ * 6: scale-factor warps, 7: epilogue warps).  For timing experiments; the output
+ * is undefined.  With a workspace of at least 64 KiB, CTA 0 logs clock64 events
+ * of its roles there. */
 #define B200_VARIANT_PROBE_BASE 100
 
 /* Library version string, e.g. "b200nvfp4 0.1 (sm_100a)". */

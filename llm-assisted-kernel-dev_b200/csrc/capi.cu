@@ -225,14 +225,12 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
                             const void* sfb2, void* c, int m, int n, int k, int l, int64_t ldc, int64_t c_batch,
                             int64_t b_batch_bytes, int64_t sfb_batch_bytes, int variant, void* workspace,
                             size_t workspace_bytes, void* stream, int device, uint32_t* status) {
-    (void)workspace;
-    (void)workspace_bytes;
     if (c_batch == 0) c_batch = static_cast<int64_t>(m) * ldc;
     if (b_batch_bytes == 0) b_batch_bytes = static_cast<int64_t>(n) * (k / 2);
     if (sfb_batch_bytes == 0) sfb_batch_bytes = static_cast<int64_t>(n / 128) * (k / 64) * 512;
     int rc = validate_dual(a, b1, b2, sfa, sfb1, sfb2, c, m, n, k, l, ldc, c_batch, b_batch_bytes, sfb_batch_bytes);
     if (rc) return rc;
-    const bool probe = variant >= B200_VARIANT_PROBE_BASE && variant < B200_VARIANT_PROBE_BASE + 64;
+    const bool probe = variant >= B200_VARIANT_PROBE_BASE && variant < B200_VARIANT_PROBE_BASE + 256;
     if (!probe && (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_SPLITK))
         return fail(B200_E_VARIANT, "dual gemm: unknown variant %d", variant);
     if (variant == B200_VARIANT_SPLITK) return fail(B200_E_VARIANT, "dual gemm: split-k variant not built");
@@ -279,6 +277,9 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     p.sf_k_atoms = k / 64;
     p.k_splits = 1;
     p.status = status ? status : st->status;
+    // timing probes: an optional 8 x 1024 x 8-byte event log for CTA 0
+    p.trace = (probe && workspace && workspace_bytes >= 8 * 1024 * sizeof(unsigned long long))
+                  ? static_cast<unsigned long long*>(workspace) : nullptr;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (probe)
@@ -425,6 +426,7 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     p.num_groups = groups;
     p.total_tiles = cur.total_tiles;
     p.status = status ? status : st->status;
+    p.trace = nullptr;
     if (variant == B200_VARIANT_SERIAL) {
         return cur.tile_n == 256 ? launch_serial<Mode::Group256>(p, p.total_tiles, 0, s)
                                  : launch_serial<Mode::Group128>(p, p.total_tiles, 0, s);

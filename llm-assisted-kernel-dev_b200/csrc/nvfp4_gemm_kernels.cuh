@@ -49,7 +49,22 @@ constexpr int kFlagSkipMma = 4;        // only the first k-block of every k-tile
 constexpr int kFlagSkipBHi = 8;        // second B tile (and its scale factors) not loaded
 constexpr int kFlagSkipStores = 16;    // epilogue drains TMEM but stores nothing
 constexpr int kFlagSkipLoads = 32;     // producer signals stages full without loading anything
+constexpr int kFlagNoSfWarps = 64;     // scale-factor warps idle, the MMA warp does not wait for them
+constexpr int kFlagNoEpilogue = 128;   // epilogue warps idle, the MMA warp does not wait for them
 
+// Event log for the timing-probe kernels: CTA 0 appends (code << 56 | clock64)
+// to its role's 1024-entry strip.
+struct Tracer {
+    unsigned long long* base;
+    int n;
+    __device__ Tracer(unsigned long long* trace, int role) : base(trace ? trace + role * 1024 : nullptr), n(0) {
+        if (blockIdx.x != 0) base = nullptr;
+    }
+    __device__ __forceinline__ void operator()(unsigned code) {
+        if (base && n < 1024) base[n++] = (static_cast<unsigned long long>(code) << 56) |
+                                          (static_cast<unsigned long long>(clock64()) & 0x00FFFFFFFFFFFFFFull);
+    }
+};
 template <Mode M> struct ModeTraits;
 template <> struct ModeTraits<Mode::Dual> {
     static constexpr int kMmaN = 256;       // accumulator columns
@@ -83,6 +98,7 @@ struct alignas(64) DenseProblem {
     long long ldc, c_batch;              // elements
     long long sfa_batch, sfb_batch;      // bytes
     float* splitk_ws;                    // fp32 partial sums (split-k variant only)
+    unsigned long long* trace;           // timing probes only: per-role clock64 event log of CTA 0
     uint32_t* splitk_flags;              // one arrival counter per output tile
     int m_tiles, n_tiles, k_tiles, batches;
     int total_tiles;                     // m_tiles * n_tiles * batches
@@ -109,6 +125,7 @@ struct GroupedProblem {
     int num_groups;
     int total_tiles;
     uint32_t* status;
+    unsigned long long* trace;           // timing probes only
 };
 
 // One unit of work: a 128-row output tile.
@@ -229,29 +246,34 @@ template <Mode M> struct StageLayout {
 };
 
 // TMEM columns (512 per SM).
-// N=256 accumulators: two buffers at columns 0 and 160 that share columns
-// [160,256); the epilogue first pulls the shared columns into registers and
+// N=256 accumulators: two buffers at columns 0 and 128 that share columns
+// [128,256); the epilogue first pulls the shared columns into registers and
 // hands them back, so the next tile's MMAs overlap with the rest of the epilogue.
 // N=128 accumulators: two disjoint buffers at 0 and 128.
-// Scale factors: a ring of eight slots, one per 64-k block (SFA 4 columns + SFB
-// kMmaN/32 columns), handed over slot by slot.  In the persistent kernel they
-// are written by four dedicated warps with tcgen05.st (shared memory ->
-// registers -> TMEM, one warp per 32-lane quadrant, which gives the 4x
+// Scale factors: a ring of slots, one per 64-k block (SFA 4 columns + SFB
+// kMmaN/32 columns), handed over kGranule slots at a time.  In the persistent
+// kernel they are written by four dedicated warps with tcgen05.st (shared memory
+// -> registers -> TMEM, one warp per 32-lane quadrant, which gives the 4x
 // replication the MMA expects for free).  A tcgen05.cp costs the tensor pipe
 // 30-60 cycles whatever its size, and NVFP4 needs twelve of them per four MMAs,
 // so copying through the tensor pipe caps it near half of its peak; the serial
-// bring-up kernel still uses tcgen05.cp.
+// bring-up kernel still uses tcgen05.cp.  The ring must cover the latency of the
+// hand-back loop (MMA retires -> commit seen by the scale-factor warps -> store
+// -> MMA warp sees the arrival, about 500 cycles): it holds 2.5 k-tiles.
 template <Mode M> struct TmemMap {
     using T = ModeTraits<M>;
     static constexpr bool kOverlapped = (T::kMmaN == 256);
-    static constexpr uint32_t kAccStride = kOverlapped ? 160 : 128;
-    static constexpr uint32_t kSharedBegin = 160;                      // columns shared by the two buffers
-    static constexpr uint32_t kSfBase = kOverlapped ? 416 : 256;
+    static constexpr uint32_t kAccStride = 128;
+    static constexpr uint32_t kSharedBegin = 128;                      // columns shared by the two buffers
+    static constexpr uint32_t kSfBase = kOverlapped ? 384 : 256;
     static constexpr uint32_t kSfBCols = T::kMmaN / 32;
     static constexpr uint32_t kSlotCols = 4 + kSfBCols;
-    static constexpr int kSlots = 8;
-    static constexpr int kEarlyChunks = kOverlapped ? 6 : 0;          // 96 shared columns / 16
+    static constexpr int kGranule = kOverlapped ? 2 : 4;              // 64-k blocks per hand-over
+    static constexpr int kBuffers = kOverlapped ? 5 : 4;              // hand-over units in the ring
+    static constexpr int kSlots = kGranule * kBuffers;
+    static constexpr int kEarlyChunks = kOverlapped ? 8 : 0;          // 128 shared columns / 16
     static_assert(kSfBase + kSlots * kSlotCols <= kTmemColumns, "TMEM budget");
+    static_assert(kKBlocks % kGranule == 0 && kBuffers <= 8, "ring shape");
     __device__ static constexpr uint32_t sfa_col(int slot) { return kSfBase + slot * kSlotCols; }
     __device__ static constexpr uint32_t sfb_col(int slot) { return kSfBase + slot * kSlotCols + 4; }
 };
@@ -261,8 +283,7 @@ struct ControlBlock {
     uint64_t empty[8];
     uint64_t acc_full[2];
     uint64_t acc_release[2];
-    uint64_t sf_ready[8];     // scale factors of one 64-k block are in TMEM slot i
-    uint64_t sf_free[8];      // the MMA that read TMEM slot i has retired
+    uint64_t sf_ready[4];     // scale factors of k-tile (i mod 4) are in TMEM
     uint64_t aux;
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
@@ -438,10 +459,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
             mbar_init(smem_u32(&ctl->acc_full[b]), 1);
             mbar_init(smem_u32(&ctl->acc_release[b]), 4);
         }
-        for (int i = 0; i < TM::kSlots; ++i) {
-            mbar_init(smem_u32(&ctl->sf_ready[i]), 4);
-            mbar_init(smem_u32(&ctl->sf_free[i]), 1);
-        }
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->sf_ready[i]), 4);
         mbar_init(smem_u32(&ctl->aux), 1);
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -458,7 +476,11 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
     const int total = S::total_units(p);
     volatile uint32_t* abort_flag = &ctl->abort_flag;
 
-    if (warp >= 6) {
+    if (kTimingProbes && warp >= 6 && (flags & kFlagNoSfWarps)) {
+        // timing probe: these warps sit the launch out
+    } else if (kTimingProbes && warp < 4 && (flags & kFlagNoEpilogue)) {
+        // timing probe: these warps sit the launch out
+    } else if (warp >= 6) {
         // ------------------------------ scale factors: shared memory -> TMEM
         // Lane r of the warp serving quadrant q reads row r of each 512-byte atom
         // (16 bytes = the row's scale factors for four 16-k blocks of four 32-row
@@ -466,18 +488,26 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
         // whole k-tile is read into registers as soon as its stage lands; each
         // 64-k block is then written the moment its ring slot is free.
         const uint32_t quad_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
-        uint32_t s = 0, ph = 0, g = 0;     // stage, its phase, running 64-k block count
+        uint32_t s = 0, ph = 0;            // stage and its phase
+        uint32_t buf = 0, use = 0;         // ring position: hand-over unit and how often it has been used
+        uint32_t units = 0;                // hand-over units written so far
+        uint32_t kt = 0;                   // k-tiles handed to the MMA warp so far
+        uint32_t retired = 0;              // k-tiles whose MMAs are known to have retired ...
+        uint32_t rs = 0, rph = 0;          // ... and the `empty` barrier that reports the next one
+        constexpr uint32_t kUnitsPerKTile = kKBlocks / TM::kGranule;
         int cursor = 0;
         bool ok = true;
         const bool skip = kTimingProbes && (flags & kFlagSkipSfCopy);
         constexpr int kAtoms = ModeTraits<M>::kHasBHi ? 3 : 2;
+        Tracer trace(kTimingProbes && lane == 0 ? p.trace : nullptr, warp == 6 ? 1 : warp - 3);   // roles 1, 4, 5, 6
         for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x) {
             const Work w = S::get(p, unit, cursor);
             for (int i = 0; ok && i < w.k_tile_count; ++i) {
-                if (!mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusSfWait)) {
+                if (!mbar_wait_warp(smem_u32(&ctl->full[s]), ph, lane, abort_flag, p.status, kStatusSfWait)) {
                     ok = false;
                     break;
                 }
+                trace(1);   // stage landed
                 uint32_t v[kKBlocks][kAtoms][4];
                 const uint32_t src = smem_base + s * L::kBytes + lane * 16;
 #pragma unroll
@@ -490,30 +520,45 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                                      v[kb][2][3]);
                 }
 #pragma unroll
-                for (int kb = 0; kb < kKBlocks; ++kb, ++g) {
-                    const int slot = g & (TM::kSlots - 1);
-                    if (g >= static_cast<uint32_t>(TM::kSlots)) {
-                        if (!mbar_wait(smem_u32(&ctl->sf_free[slot]), ((g >> 3) - 1u) & 1u, abort_flag, p.status,
-                                       kStatusSfWait)) {
-                            ok = false;
-                            break;
+                for (int gr = 0; gr < kKBlocks / TM::kGranule; ++gr, ++units) {
+                    // The unit's previous contents were read by the MMAs of k-tile
+                    // (units - kBuffers) / kUnitsPerKTile; the stage's `empty` barrier
+                    // (one tcgen05.commit per k-tile) says when those have retired.
+                    if (units >= static_cast<uint32_t>(TM::kBuffers)) {
+                        const uint32_t need = (units - TM::kBuffers) / kUnitsPerKTile;
+                        while (ok && retired <= need) {
+                            ok = mbar_wait_warp(smem_u32(&ctl->empty[rs]), rph, lane, abort_flag, p.status,
+                                                kStatusSfWait);
+                            ++retired;
+                            if (++rs == kStages) { rs = 0; rph ^= 1u; }
                         }
+                        if (!ok) break;
                         tc_fence_after_sync();
                     }
-                    if (!skip || g < static_cast<uint32_t>(TM::kSlots)) {
-                        tc_st_x4(tmem_base + quad_lane + TM::sfa_col(slot), v[kb][0][0], v[kb][0][1], v[kb][0][2],
-                                 v[kb][0][3]);
-                        tc_st_x4(tmem_base + quad_lane + TM::sfb_col(slot), v[kb][1][0], v[kb][1][1], v[kb][1][2],
-                                 v[kb][1][3]);
-                        if constexpr (kAtoms == 3)
-                            tc_st_x4(tmem_base + quad_lane + TM::sfb_col(slot) + 4, v[kb][2][0], v[kb][2][1],
-                                     v[kb][2][2], v[kb][2][3]);
+                    trace(2);   // ring unit free
+                    if (!skip || use == 0) {
+#pragma unroll
+                        for (int q = 0; q < TM::kGranule; ++q) {
+                            const int kb = gr * TM::kGranule + q;
+                            const int slot = buf * TM::kGranule + q;
+                            tc_st_x4(tmem_base + quad_lane + TM::sfa_col(slot), v[kb][0][0], v[kb][0][1], v[kb][0][2],
+                                     v[kb][0][3]);
+                            tc_st_x4(tmem_base + quad_lane + TM::sfb_col(slot), v[kb][1][0], v[kb][1][1], v[kb][1][2],
+                                     v[kb][1][3]);
+                            if constexpr (kAtoms == 3)
+                                tc_st_x4(tmem_base + quad_lane + TM::sfb_col(slot) + 4, v[kb][2][0], v[kb][2][1],
+                                         v[kb][2][2], v[kb][2][3]);
+                        }
                         tc_wait_st();
                     }
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_ready[slot]));
+                    if (++buf == TM::kBuffers) { buf = 0; ++use; }
                 }
+                if (!ok) break;
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_ready[kt & 3u]));
+                trace(3);   // k-tile handed to the MMA warp
+                ++kt;
                 if (++s == kStages) { s = 0; ph ^= 1u; }
             }
         }
@@ -523,6 +568,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
             uint32_t s = 0, ph = 0;
             int cursor = 0, last_group = -1;
             bool ok = true;
+            Tracer trace(kTimingProbes ? p.trace : nullptr, 2);
             for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x) {
                 const Work w = S::get(p, unit, cursor);
                 if (M != Mode::Dual && w.group != last_group) {
@@ -531,10 +577,12 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                     last_group = w.group;
                 }
                 for (int i = 0; i < w.k_tile_count; ++i) {
-                    if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status, kStatusProducerWait)) {
+                    if (!mbar_wait<true>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
+                                         kStatusProducerWait)) {
                         ok = false;
                         break;
                     }
+                    trace(1);   // stage free, loads issued
                     issue_stage_loads<M, kTimingProbes>(w, w.k_tile_begin + i, smem_base + s * L::kBytes,
                                                         smem_u32(&ctl->full[s]), flags);
                     if (++s == kStages) { s = 0; ph ^= 1u; }
@@ -548,47 +596,73 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
         __syncwarp();
     } else if (warp == 4) {
         // ------------------------------ MMA issuer
+        // One thread issues every MMA of the CTA.  Each tcgen05.mma, tcgen05.commit
+        // and mbarrier.try_wait costs that thread about 50 cycles, and four MMAs
+        // occupy the tensor pipe for 520: the loop has room for four MMAs, one wait
+        // and one commit per k-tile and little else.  So: one wait per k-tile (on
+        // the scale factors; their writers waited for the stage's `full` barrier
+        // before reading the stage, which orders the operand bytes before these
+        // MMAs too), one commit per k-tile, 32-bit descriptor words advanced by
+        // constants, counters kept incrementally.
         if (lane == 0) {
-            uint32_t s = 0, ph = 0, g = 0;   // stage, its phase, running 64-k block count
+            using T = ModeTraits<M>;
+            constexpr uint32_t kUnitCols = TM::kGranule * TM::kSlotCols;
+            const uint32_t desc_lo_base = smem_desc_lo(smem_base + L::kOffA);
+            const uint32_t sf_ready_bar = smem_u32(&ctl->sf_ready[0]);
+            const uint32_t empty_bar = smem_u32(&ctl->empty[0]);
+            const uint32_t sf_base = tmem_base + TM::kSfBase;
+            uint32_t s = 0, a_lo = desc_lo_base;   // stage and the low word of its A descriptor
+            uint32_t kt = 0;                       // running k-tile count
+            uint32_t buf = 0;                      // scale-factor ring unit
             int cursor = 0, it = 0;
-            const bool two_mma = (flags & kFlagTwoMma) != 0;
+            bool failed = false;
             const int mma_blocks = (kTimingProbes && (flags & kFlagSkipMma)) ? 1 : kKBlocks;
-            bool ok = true;
-            for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x, ++it) {
+            const bool no_sf = kTimingProbes && (flags & kFlagNoSfWarps);
+            const bool no_epi = kTimingProbes && (flags & kFlagNoEpilogue);
+            Tracer trace(kTimingProbes ? p.trace : nullptr, 0);
+            for (int unit = blockIdx.x; unit < total; unit += gridDim.x, ++it) {
                 const Work w = S::get(p, unit, cursor);
-                if (it > 0) {
+                if (it > 0 && !no_epi) {
                     const int r = it - 1;   // wait for hand-back number r
                     if (!mbar_wait(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
                                    kStatusMmaWaitAcc)) {
-                        ok = false;
+                        failed = true;
                         break;
                     }
                     tc_fence_after_sync();
                 }
-                const uint32_t acc_col = (it & 1) * TM::kAccStride;
-                for (int i = 0; ok && i < w.k_tile_count; ++i) {
-                    if (!mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusMmaWaitFull)) {
-                        ok = false;
+                trace(9);   // accumulator buffer available
+                const uint32_t acc_addr = tmem_base + (it & 1) * TM::kAccStride;
+                const int k_tiles = w.k_tile_count;
+#pragma unroll 1
+                for (int i = 0; i < k_tiles; ++i) {
+                    const uint32_t bar = no_sf ? smem_u32(&ctl->full[s]) : sf_ready_bar + (kt & 3u) * 8u;
+                    const uint32_t parity = no_sf ? (kt / kStages) & 1u : (kt >> 2) & 1u;
+                    if (!mbar_wait(bar, parity, abort_flag, p.status, kStatusMmaWaitFull)) {
+                        failed = true;
                         break;
                     }
-                    const uint32_t stage = smem_base + s * L::kBytes;
+                    tc_fence_after_sync();
+                    trace(1);   // k-tile ready
 #pragma unroll
-                    for (int kb = 0; kb < kKBlocks; ++kb, ++g) {
-                        const int slot = g & (TM::kSlots - 1);
-                        if (!mbar_wait(smem_u32(&ctl->sf_ready[slot]), (g >> 3) & 1u, abort_flag, p.status,
-                                       kStatusMmaWaitFull)) {
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        if (kb < mma_blocks)
-                            issue_mma<M>(stage, tmem_base, acc_col, kb, slot, (i > 0 || kb > 0) ? 1u : 0u, two_mma);
-                        tc_commit(smem_u32(&ctl->sf_free[slot]));   // slot reusable once this MMA retires
+                    for (int kb = 0; kb < kKBlocks; ++kb) {
+                        if (kb > 0 && kb % TM::kGranule == 0) buf = (buf + 1 == TM::kBuffers) ? 0u : buf + 1;
+                        if (kTimingProbes && kb >= mma_blocks) continue;
+                        const uint32_t sfa = sf_base + buf * kUnitCols + (kb % TM::kGranule) * TM::kSlotCols;
+                        tc_mma_mxf4nvf4_lo(acc_addr, a_lo + 2 * kb, a_lo + (L::kOffBLo >> 4) + 2 * kb,
+                                           idesc_mxf4nvf4(128, T::kMmaN), sfa, sfa + 4, (kb > 0 || i > 0) ? 1u : 0u);
                     }
-                    tc_commit(smem_u32(&ctl->empty[s]));            // stage reusable once these MMAs retire
-                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                    buf = (buf + 1 == TM::kBuffers) ? 0u : buf + 1;
+                    // one commit per k-tile: frees the stage for the producer and tells the
+                    // scale-factor warps that the ring units this k-tile read are reusable
+                    tc_commit(empty_bar + s * 8);
+                    ++kt;
+                    ++s;
+                    a_lo += L::kBytes >> 4;
+                    if (s == kStages) { s = 0; a_lo = desc_lo_base; }
                 }
-                if (ok) tc_commit(smem_u32(&ctl->acc_full[it & 1]));
+                if (failed) break;
+                tc_commit(smem_u32(&ctl->acc_full[it & 1]));
             }
             // drain: every MMA issued above must retire before TMEM is freed
             tc_commit(smem_u32(&ctl->aux));
@@ -599,6 +673,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
         // ------------------------------ epilogue warps 0-3
         int cursor = 0, it = 0;
         bool ok = true;
+        Tracer trace(kTimingProbes && warp == 0 && lane == 0 ? p.trace : nullptr, 3);
         for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x, ++it) {
             const Work w = S::get(p, unit, cursor);
             const uint32_t release_bar = smem_u32(&ctl->acc_release[it & 1]);
@@ -607,17 +682,19 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                 __syncwarp();
                 if (lane == 0) mbar_arrive(release_bar);
             }
-            if (!mbar_wait(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
-                           kStatusEpilogueWait)) {
+            if (!mbar_wait_warp(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, lane, abort_flag, p.status,
+                                kStatusEpilogueWait)) {
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
+            trace(1);   // accumulator complete
             const bool store = !(kTimingProbes && (flags & kFlagSkipStores));
             if (it & 1)
                 epilogue_tile<M, 1>(w, tmem_base, warp, lane, release_bar, store);
             else
                 epilogue_tile<M, 0>(w, tmem_base, warp, lane, release_bar, store);
+            trace(2);   // tile stored
             tc_fence_before_sync();
         }
     }

@@ -79,6 +79,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait that lets the hardware park the thread for up to `hint_ns` before it
+// reports "not yet": far fewer barrier accesses than a tight polling loop.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait: gives up after about a second (kWaitTimeoutCycles SM clocks),
 // ORs `code` into *status, raises the CTA-wide abort flag and returns false.
 // Never traps, never spins forever.  The deadline is kept with clock64(), which
@@ -86,6 +102,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // wake-up path of every wait that does not succeed at once.
 constexpr long long kWaitTimeoutCycles = 2000ll * 1000ll * 1000ll;
 
+template <bool kParked = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -94,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     while (true) {
 #pragma unroll 1
         for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
+            if (kParked ? mbar_try_wait_parked(bar, parity, 20000u) : mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > kWaitTimeoutCycles) {
             *abort_flag = 1u;
@@ -102,6 +119,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             return false;
         }
     }
+}
+
+// Warp-wide bounded wait: lane 0 polls, the outcome is broadcast.  Every polling
+// lane is a separate access to the barrier, and barrier traffic from waiting
+// warps slows down the (single) thread that issues the MMAs on the same SM.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int lane, volatile uint32_t* abort_flag,
+                                               uint32_t* status, uint32_t code) {
+    uint32_t ok = 1;
+    if (lane == 0) ok = mbar_wait<true>(bar, parity, abort_flag, status, code) ? 1u : 0u;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -215,6 +242,30 @@ __device__ __forceinline__ void tc_mma_mxf4nvf4(uint32_t tmem_d, uint64_t adesc,
         "}\n"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tmem_sfa),
         "r"(tmem_sfb)
+        : "memory");
+}
+
+// Same MMA, operands given as the low words of their SWIZZLE_128B descriptors (the
+// high word is the same constant for every operand tile): keeps the issuing
+// thread's dependent instruction chain short.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO, version, layout
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) {
+    return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);                       // start address, LBO = 1
+}
+__device__ __forceinline__ void tc_mma_mxf4nvf4_lo(uint32_t tmem_d, uint32_t adesc_lo, uint32_t bdesc_lo,
+                                                   uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                                   uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %7};\n\t"
+        "mov.b64 db, {%2, %7};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "r"(adesc_lo), "r"(bdesc_lo), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb),
+        "r"(kDescHiSw128)
         : "memory");
 }
 
