@@ -128,6 +128,34 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
 
 size_t b200_grouped_workspace_bytes(int groups);
 
+/*
+ * Grouped GEMM for callers that have no device memory to give and may not
+ * allocate any.  No counterpart in the reference: there, PyTorch's allocator is
+ * always at hand.  A serving engine that has handed every byte of the GPU to its
+ * own pools, a plugin running inside someone else's memory budget, or code on a
+ * path where cudaMalloc's implicit device synchronisation is unacceptable has
+ * nowhere to put the per-group descriptor table that b200_grouped_gemm_nvfp4
+ * keeps in the caller's workspace.  Here the table lives in a fixed array inside
+ * the library's device image instead: B200_STATIC_MAX_GROUPS entries of 384
+ * bytes (24 KiB), present on every GPU that loads the library until the process
+ * exits.  Arguments and results are those of b200_grouped_gemm_nvfp4 without the
+ * workspace; the same kernels run.
+ *
+ *  - groups > B200_STATIC_MAX_GROUPS is rejected with B200_E_LIMIT.
+ *  - The call allocates and frees nothing, on the device or through any library.
+ *  - The first call on a device looks up the array's device address and does the
+ *    library's one-time per-device set-up; make that call before any stream
+ *    capture begins.
+ *  - Every call rewrites the entries it uses and all calls share the one array:
+ *    two calls whose GPU work can overlap (different streams, or the same stream
+ *    from different threads without ordering) race on it.  Calls on one stream
+ *    are safe back to back.
+ */
+#define B200_STATIC_MAX_GROUPS 64
+int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void* const* b,
+                                   const void* const* sfa, const void* const* sfb, void* const* c,
+                                   const int* mnk, void* stream, int device, uint32_t* status);
+
 /* Synchronise `stream`, copy the library-owned status word of `device` into
  * *out and clear it. */
 int b200_read_status(int device, void* stream, uint32_t* out);

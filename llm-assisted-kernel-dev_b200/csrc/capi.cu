@@ -443,6 +443,118 @@ int b200_grouped_gemm_nvfp4(int groups, const void* const* a, const void* const*
                                       0, stream, device, status);
 }
 
+}  // extern "C"
+
+namespace b200 {
+namespace {
+// Descriptor table of the entry point that may not allocate: part of the
+// library's device image, so it exists on every GPU the library is loaded on.
+// In host code this name is only a handle for cudaGetSymbolAddress; the kernels
+// get the device address looked up below.
+static __device__ __align__(256) GroupEntry g_static_group_table[B200_STATIC_MAX_GROUPS];
+
+constexpr int kMaxDevices = 64;
+GroupEntry* g_static_table_addr[kMaxDevices] = {};   // per device, filled on first use
+
+// Device address of the table on the current device (`device` must be current).
+int static_table_address(int device, GroupEntry** out) {
+    if (device < 0 || device >= kMaxDevices) return fail(B200_E_LIMIT, "device index %d out of range", device);
+    if (!g_static_table_addr[device]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_group_table);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_static_group_table)");
+        g_static_table_addr[device] = static_cast<GroupEntry*>(ptr);
+    }
+    *out = g_static_table_addr[device];
+    return 0;
+}
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
+int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void* const* b, const void* const* sfa,
+                                   const void* const* sfb, void* const* c, const int* mnk, void* stream, int device,
+                                   uint32_t* status) {
+    if (groups <= 0) return fail(B200_E_SHAPE, "grouped gemm (static table): groups=%d must be positive", groups);
+    if (groups > B200_STATIC_MAX_GROUPS)
+        return fail(B200_E_LIMIT,
+                    "grouped gemm (static table): %d groups exceed the built-in table of %d entries; use "
+                    "b200_grouped_gemm_nvfp4 with a workspace, or split the call",
+                    groups, B200_STATIC_MAX_GROUPS);
+    if (!a || !b || !sfa || !sfb || !c || !mnk)
+        return fail(B200_E_NULL, "grouped gemm (static table): NULL argument array");
+    bool all_n256 = true;
+    long long tiles128 = 0;
+    for (int g = 0; g < groups; ++g) {
+        const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
+        if (m < 0 || n <= 0 || k <= 0)
+            return fail(B200_E_SHAPE, "grouped gemm (static table): group %d has invalid shape (%d, %d, %d)", g, m, n,
+                        k);
+        if (n % 128) return fail(B200_E_SHAPE, "grouped gemm (static table): group %d n=%d is not a multiple of 128", g, n);
+        if (k % 256) return fail(B200_E_SHAPE, "grouped gemm (static table): group %d k=%d is not a multiple of 256", g, k);
+        if (m == 0) continue;
+        if (!a[g] || !b[g] || !sfa[g] || !sfb[g] || !c[g])
+            return fail(B200_E_NULL, "grouped gemm (static table): group %d has a NULL tensor pointer", g);
+        if (!aligned16(a[g]) || !aligned16(b[g]) || !aligned16(sfa[g]) || !aligned16(sfb[g]) || !aligned16(c[g]))
+            return fail(B200_E_ALIGN, "grouped gemm (static table): group %d has a pointer that is not 16-byte aligned",
+                        g);
+        if (n % 256) all_n256 = false;
+        tiles128 += static_cast<long long>((m + 127) / 128) * (n / 128);
+    }
+    if (tiles128 == 0) return 0;
+
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    int rc;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;        // one-time per-device set-up, no allocation
+    GroupEntry* table_dev = nullptr;
+    if ((rc = static_table_address(device, &table_dev))) return rc;
+
+    const int tile_n = (all_n256 && tiles128 / 2 >= 2LL * st->sm_count) ? 256 : 128;
+    // Host copy of the table on the stack (24 KiB at most): nothing is allocated.
+    GroupEntry table[B200_STATIC_MAX_GROUPS];
+    memset(table, 0, static_cast<size_t>(groups) * sizeof(GroupEntry));
+    int tile_begin = 0;
+    for (int g = 0; g < groups; ++g) {
+        const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
+        GroupEntry& e = table[g];
+        e.m = m;
+        e.n = n;
+        e.k_tiles = k / 256;
+        e.m_tiles = (m + 127) / 128;
+        e.n_tiles = (n + tile_n - 1) / tile_n;
+        e.tile_begin = tile_begin;
+        e.sf_k_atoms = k / 64;
+        e.sfb_row_atoms = n / 128;
+        e.ldc = n;
+        tile_begin += e.m_tiles * e.n_tiles;
+        if (m == 0) continue;
+        e.sfa = static_cast<const uint8_t*>(sfa[g]);
+        e.sfb = static_cast<const uint8_t*>(sfb[g]);
+        e.c = static_cast<__half*>(c[g]);
+        if ((rc = encode_operand_map(&e.map_a, a[g], m, k, 1, static_cast<long long>(m) * (k / 2)))) return rc;
+        if ((rc = encode_operand_map(&e.map_b, b[g], n, k, 1, static_cast<long long>(n) * (k / 2)))) return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Every entry this launch reads is rewritten here, so nothing left by an earlier
+    // call is ever consumed; entries beyond `groups` keep stale bytes and are not read.
+    // The source is pageable stack memory: the runtime has copied it out by the time
+    // this returns, so `table` may die while the transfer is still queued on `s`.
+    B200_CUDA(cudaMemcpyAsync(table_dev, table, static_cast<size_t>(groups) * sizeof(GroupEntry),
+                              cudaMemcpyHostToDevice, s));
+    GroupedProblem p;
+    p.groups = table_dev;
+    p.num_groups = groups;
+    p.total_tiles = tile_begin;
+    p.status = status ? status : st->status;
+    p.trace = nullptr;
+    return tile_n == 256 ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s)
+                         : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s);
+}
+
 int b200_read_status(int device, void* stream, uint32_t* out) {
     if (!out) return fail(B200_E_NULL, "read_status: out is NULL");
     std::lock_guard<std::mutex> lock(g_mutex);

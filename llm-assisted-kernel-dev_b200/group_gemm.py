@@ -97,3 +97,30 @@ def custom_kernel(data, *, variant: int = _lib.VARIANT_AUTO, tile_n: int = 0, ev
     (group_gemm/group_gemm_cute5_v2.py:4245-4251) and ignored."""
     abc_tensors, _, sfasfb_reordered_tensors, problem_sizes = data
     return grouped_gemm(abc_tensors, sfasfb_reordered_tensors, problem_sizes, variant=variant, tile_n=tile_n)
+
+
+def custom_kernel_no_alloc(data):
+    """Same contract as ``custom_kernel`` for callers that must not allocate
+    device memory: the per-group descriptor table lives in a fixed array inside
+    the library instead of a workspace tensor, so this wrapper creates no
+    tensors at all.  At most ``_lib.STATIC_MAX_GROUPS`` groups; calls whose GPU
+    work may overlap must not use this entry point concurrently (they share the
+    one table).  The first call on a device should precede any stream capture."""
+    abc_tensors, _, sf_perm, problem_sizes = data
+    g = len(problem_sizes)
+    if g == 0:
+        raise ValueError("grouped gemm needs at least one group")
+    dev = abc_tensors[0][2].device
+    if dev.type != "cuda":
+        raise ValueError("grouped gemm needs CUDA tensors (there is no CPU path)")
+    arr = ctypes.c_void_p * g
+    a, b, c, sfa, sfb = arr(), arr(), arr(), arr(), arr()
+    mnk = (ctypes.c_int * (3 * g))()
+    for i, ((ta, tb, tc), (tsfa, tsfb), (m, n, k, l)) in enumerate(zip(abc_tensors, sf_perm, problem_sizes)):
+        if l != 1:
+            raise ValueError(f"group {i}: l={l}; the grouped path supports l == 1 only")
+        a[i], b[i], c[i], sfa[i], sfb[i] = ta.data_ptr(), tb.data_ptr(), tc.data_ptr(), tsfa.data_ptr(), tsfb.data_ptr()
+        mnk[3 * i], mnk[3 * i + 1], mnk[3 * i + 2] = m, n, k
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(_lib.load().b200_grouped_gemm_nvfp4_static(g, a, b, sfa, sfb, c, mnk, stream, dev.index, None))
+    return [tc for (_ta, _tb, tc) in abc_tensors]
