@@ -82,16 +82,25 @@ int b200_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const vo
                          const void* sfb1, const void* sfb2, void* c, int m, int n, int k, int l,
                          int64_t ldc, void* stream, int device, uint32_t* status);
 
-/* Same, with explicit batch strides, kernel variant and (for
- * B200_VARIANT_SPLITK, else may be NULL/0) an fp32 partial-sum workspace of
- * b200_dual_splitk_workspace_bytes() bytes, 256-byte aligned. */
+/* Same, with explicit batch strides, kernel variant and an optional split-k
+ * workspace (256-byte aligned, b200_dual_splitk_workspace_bytes() bytes).  Shapes
+ * with fewer than half as many 128x128 output tiles as the GPU has SMs are cut
+ * along k so that every SM gets a piece; the pieces exchange fp32 partial sums
+ * through the workspace before the silu*mul epilogue.  Only B200_VARIANT_SPLITK
+ * splits (and fails without a large enough workspace); the other variants ignore
+ * the workspace.  The first bytes of the workspace hold
+ * per-unit flag words that each launch stamps with a fresh number: zero-fill the
+ * workspace once before its first use.  One workspace per stream.  The units of
+ * a tile wait for one another inside the launch, so the library never starts
+ * more units than the GPU has SMs. */
 int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const void* sfa,
                             const void* sfb1, const void* sfb2, void* c, int m, int n, int k, int l,
                             int64_t ldc, int64_t c_batch, int64_t b_batch_bytes,
                             int64_t sfb_batch_bytes, int variant, void* workspace,
                             size_t workspace_bytes, void* stream, int device, uint32_t* status);
 
-/* Bytes of workspace the split-k variant needs for an (m, n, k, l) problem. */
+/* Bytes of split-k workspace for an (m, n, k, l) problem on a 148-SM B200;
+ * 0 when the shape has enough tiles and is not split. */
 size_t b200_dual_splitk_workspace_bytes(int m, int n, int k, int l);
 
 /*

@@ -18,6 +18,7 @@ namespace {
 thread_local std::string t_last_error;
 std::mutex g_mutex;
 uint64_t g_launches = 0;
+uint64_t g_epoch = 0;                  // split-k launches so far (their flag value)
 
 __device__ uint32_t g_device_status;   // library-owned status word (one per device)
 
@@ -185,6 +186,24 @@ int validate_dual(const void* a, const void* b1, const void* b2, const void* sfa
     return 0;
 }
 
+// Split-k factor for a dual GEMM with `tiles` output tiles of `k_tiles` k-tiles on
+// `sms` SMs: as many units as fit in one wave, at least four k-tiles per unit.
+int split_count(int tiles, int k_tiles, int sms) {
+    if (tiles * 2 > sms) return 1;
+    int s = sms / tiles;
+    if (s > k_tiles / 4) s = k_tiles / 4;
+    if (s > 8) s = 8;
+    // every unit must own at least one k-tile when the range is cut into ceil(k_tiles / s) pieces
+    while (s > 1 && (s - 1) * ((k_tiles + s - 1) / s) >= k_tiles) --s;
+    return s < 1 ? 1 : s;
+}
+size_t splitk_bytes(size_t tiles, int splits);
+size_t splitk_flag_bytes(size_t tiles) { return (tiles * 8 * sizeof(uint32_t) + 255) & ~static_cast<size_t>(255); }
+// epoch words (eight per tile) followed by the fp32 partial sums
+size_t splitk_bytes(size_t tiles, int splits) {
+    return splits <= 1 ? 0 : splitk_flag_bytes(tiles) + tiles * splits * 128 * 256 * sizeof(float);
+}
+
 template <Mode M, int kStages, typename P, bool kTimingProbes = false>
 int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStream_t stream) {
     const int grid = units < sm_count ? units : sm_count;
@@ -216,9 +235,10 @@ const char* b200_last_error(void) { return t_last_error.c_str(); }
 uint64_t b200_launch_count(void) { return g_launches; }
 
 size_t b200_dual_splitk_workspace_bytes(int m, int n, int k, int l) {
-    (void)k;
-    if (m <= 0 || n <= 0 || l <= 0) return 0;
-    return 0;
+    if (m <= 0 || n <= 0 || k <= 0 || l <= 0 || m % 128 || n % 128 || k % 256) return 0;
+    const size_t tiles = static_cast<size_t>(m / 128) * (n / 128) * l;
+    const int splits = split_count(static_cast<int>(tiles > 1000000 ? 1000000 : tiles), k / 256, 148);
+    return splitk_bytes(tiles, splits);
 }
 
 int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
@@ -233,7 +253,6 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     const bool probe = variant >= B200_VARIANT_PROBE_BASE && variant < B200_VARIANT_PROBE_BASE + 256;
     if (!probe && (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_SPLITK))
         return fail(B200_E_VARIANT, "dual gemm: unknown variant %d", variant);
-    if (variant == B200_VARIANT_SPLITK) return fail(B200_E_VARIANT, "dual gemm: split-k variant not built");
 
     std::lock_guard<std::mutex> lock(g_mutex);
     DeviceGuard guard;
@@ -285,6 +304,24 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     if (probe)
         return launch_persistent<Mode::Dual, kDualStages, DenseProblem, true>(p, p.total_tiles, st->sm_count,
                                                                               variant - B200_VARIANT_PROBE_BASE, s);
+    // Split-k only on request (B200_VARIANT_SPLITK): its partial-sum exchange through
+    // global memory currently costs more than the idle SMs it puts to work.
+    if (variant == B200_VARIANT_SPLITK) {
+        const int splits = split_count(p.total_tiles, p.k_tiles, st->sm_count);
+        const size_t need = splitk_bytes(static_cast<size_t>(p.total_tiles), splits);
+        if (splits > 1 && workspace && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 255u)) {
+            p.k_splits = splits;
+            // any value no earlier launch has used; the workspace starts zero-filled
+            p.splitk_epoch = static_cast<uint32_t>(++g_epoch);
+            if (p.splitk_epoch == 0) p.splitk_epoch = static_cast<uint32_t>(++g_epoch);
+            p.splitk_flags = static_cast<uint32_t*>(workspace);
+            p.splitk_ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + splitk_flag_bytes(p.total_tiles));
+        } else if (variant == B200_VARIANT_SPLITK && splits > 1) {
+            return fail(B200_E_WORKSPACE, "dual gemm: split-k needs a 256-byte aligned workspace of %zu bytes", need);
+        }
+    }
+    if (p.k_splits > 1)
+        return launch_persistent<Mode::Dual, kDualStages>(p, p.total_tiles * p.k_splits, st->sm_count, 0, s);
     switch (variant) {
         case B200_VARIANT_SERIAL:
             return launch_serial<Mode::Dual>(p, p.total_tiles, 0, s);

@@ -99,7 +99,8 @@ struct alignas(64) DenseProblem {
     long long sfa_batch, sfb_batch;      // bytes
     float* splitk_ws;                    // fp32 partial sums (split-k variant only)
     unsigned long long* trace;           // timing probes only: per-role clock64 event log of CTA 0
-    uint32_t* splitk_flags;              // one arrival counter per output tile
+    uint32_t* splitk_flags;              // eight epoch words per output tile (one per unit)
+    uint32_t splitk_epoch;               // value that marks "written during this launch"
     int m_tiles, n_tiles, k_tiles, batches;
     int total_tiles;                     // m_tiles * n_tiles * batches
     int sf_k_atoms;                      // k / 64
@@ -284,7 +285,7 @@ struct ControlBlock {
     uint64_t acc_full[2];
     uint64_t acc_release[2];
     uint64_t sf_ready[4];     // scale factors of k-tile (i mod 4) are in TMEM
-    uint64_t aux;
+    uint64_t aux[2];
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 };
@@ -427,15 +428,123 @@ __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base,
     }
 }
 
+// Split-k epilogue (dual GEMM with few output tiles): a tile's k range is cut into
+// `k_splits` units that run on different CTAs at the same time (the host never
+// launches more units than there are SMs, one CTA per SM).  Output column chunk c
+// (16 columns) is finished by unit c % k_splits: every unit writes the fp32
+// partial sums of the chunks it does not own to the workspace, publishes a flag,
+// waits (bounded) for its peers' flags and adds their partial sums of its own
+// chunks to its accumulator in unit order, so the result does not depend on
+// timing.  Each unit runs 1/k_splits of the silu*mul epilogue.
+// Workspace: flags[tile][8] (uint32, written with the launch's epoch, never reset)
+// then per (tile, unit) 128 KiB laid out [chunk][x|y][quarter][row][4 floats] so
+// that a warp's stores and loads are contiguous.
+template <int kBuf>
+__device__ __forceinline__ bool epilogue_tile_splitk(const DenseProblem& p, const Work& w, uint32_t tmem_base,
+                                                     int quad, int lane, uint32_t release_bar,
+                                                     volatile uint32_t* abort_flag) {
+    using TM = TmemMap<Mode::Dual>;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
+    const int row = quad * 32 + lane;
+    const int splits = p.k_splits;
+    const size_t unit_floats = static_cast<size_t>(kTileM) * 256;
+    float* tile_ws = p.splitk_ws + static_cast<size_t>(w.tile) * splits * unit_floats;
+    float* mine = tile_ws + static_cast<size_t>(w.split) * unit_floats + row * 4;
+    uint32_t* flags = p.splitk_flags + static_cast<size_t>(w.tile) * 8;
+    // ---- send the chunks other units own
+#pragma unroll 1
+    for (int chunk = 0; chunk < 8; ++chunk) {
+        if (chunk % splits == w.split) continue;
+        uint32_t x[16], y[16];
+        tc_ld_x16(acc + chunk * 16, x);
+        tc_ld_x16(acc + 128 + chunk * 16, y);
+        tc_wait_ld();
+        float* dst = mine + static_cast<size_t>(chunk) * 8 * (kTileM * 4);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            st_global_v4f(dst + q * (kTileM * 4), x[4 * q], x[4 * q + 1], x[4 * q + 2], x[4 * q + 3]);
+            st_global_v4f(dst + (4 + q) * (kTileM * 4), y[4 * q], y[4 * q + 1], y[4 * q + 2], y[4 * q + 3]);
+        }
+    }
+    __threadfence();
+    epilogue_bar_sync();
+    if (threadIdx.x == 0) st_release_gpu_u32(flags + w.split, p.splitk_epoch);
+    // ---- wait for the peers (lane 0 polls; bounded)
+    uint32_t ok = 1;
+    if (lane == 0) {
+        const long long t0 = clock64();
+        for (int peer = 0; peer < splits && ok; ++peer) {
+            if (peer == w.split) continue;
+            while (ld_acquire_gpu_u32(flags + peer) != p.splitk_epoch) {
+                if (*abort_flag || clock64() - t0 > kWaitTimeoutCycles) {
+                    *abort_flag = 1u;
+                    atomicOr(p.status, kStatusSplitKWait);
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) {
+        __half* row_ptr = w.c + static_cast<long long>(row) * w.ldc;
+#pragma unroll 1
+        for (int chunk = w.split; chunk < 8; chunk += splits) {
+            uint32_t xb[16], yb[16];
+            tc_ld_x16(acc + chunk * 16, xb);
+            tc_ld_x16(acc + 128 + chunk * 16, yb);
+            float x[16], y[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = y[i] = 0.0f;
+            bool own_added = false;
+            for (int unit = 0; unit < splits; ++unit) {
+                if (unit == w.split) {
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { x[i] += __uint_as_float(xb[i]); y[i] += __uint_as_float(yb[i]); }
+                    own_added = true;
+                    continue;
+                }
+                const float* src = tile_ws + static_cast<size_t>(unit) * unit_floats + row * 4 +
+                                   static_cast<size_t>(chunk) * 8 * (kTileM * 4);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 a = ld_global_cg_v4f(src + q * (kTileM * 4));
+                    const float4 b = ld_global_cg_v4f(src + (4 + q) * (kTileM * 4));
+                    x[4 * q] += a.x; x[4 * q + 1] += a.y; x[4 * q + 2] += a.z; x[4 * q + 3] += a.w;
+                    y[4 * q] += b.x; y[4 * q + 1] += b.y; y[4 * q + 2] += b.z; y[4 * q + 3] += b.w;
+                }
+            }
+            if (!own_added) tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { xb[i] = __float_as_uint(x[i]); yb[i] = __float_as_uint(y[i]); }
+            store_chunk<true>(row_ptr, chunk, xb, yb);
+        }
+    }
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(release_bar);       // accumulator drained: the MMA warp may reuse it
+    return ok != 0;
+}
+
 // ---------------------------------------------------------------------------
 // Persistent warp-specialised kernel: 10 warps.
 //   warps 0-3  epilogue (TMEM lane quadrants 0-3)
-//   warp 4     TMEM allocation + MMA issue (one lane)
+//   warp 4     TMEM allocation + first MMA issuer (one lane)
 //   warp 5     TMA producer (one lane)
 //   warps 6-9  scale factors shared memory -> TMEM (quadrants 2, 3, 0, 1)
 // CTA b walks work units b, b+grid, b+2*grid, ...
 // ---------------------------------------------------------------------------
-constexpr int kPersistentThreads = 320;
+// MMA-issuing threads.  Two issuers (warps 4 and 10, taking turns k-tile by k-tile)
+// were measured and bring nothing: the limit is not the issuing thread.
+constexpr int kIssuers = 1;
+// Sets of four scale-factor warps that take turns k-tile by k-tile.  Two sets (16
+// warps, registers rebalanced per warpgroup with setmaxnreg) were measured: the
+// scale-factor hand-over gets faster but loads, epilogue and launch overhead get
+// slower by more.
+constexpr int kSfSets = 1;
+constexpr int kFirstSfWarp = kSfSets == 2 ? 8 : 6;
+constexpr int kPersistentThreads = 32 * (kFirstSfWarp + 4 * kSfSets);
 
 template <Mode M, int kStages, bool kTimingProbes = false>
 __global__ void __launch_bounds__(kPersistentThreads, 1)
@@ -456,11 +565,12 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&ctl->acc_full[b]), 1);
+            mbar_init(smem_u32(&ctl->acc_full[b]), kIssuers);   // every MMA issuer commits
             mbar_init(smem_u32(&ctl->acc_release[b]), 4);
         }
         for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->sf_ready[i]), 4);
-        mbar_init(smem_u32(&ctl->aux), 1);
+        mbar_init(smem_u32(&ctl->aux[0]), 1);
+        mbar_init(smem_u32(&ctl->aux[1]), 1);
         ctl->abort_flag = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
@@ -476,12 +586,25 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
     const int total = S::total_units(p);
     volatile uint32_t* abort_flag = &ctl->abort_flag;
 
-    if (kTimingProbes && warp >= 6 && (flags & kFlagNoSfWarps)) {
+    // Register budget per warpgroup (512 threads start with 128 each): the epilogue
+    // holds 128 accumulator columns in registers, everybody else needs few.
+    if constexpr (kSfSets == 2) {
+        if (warp < 4) warpgroup_reg_inc<168>();
+        else if (warp < 8) warpgroup_reg_dec<120>();
+        else warpgroup_reg_dec<112>();
+    }
+
+    if (kTimingProbes && warp >= kFirstSfWarp && (flags & kFlagNoSfWarps)) {
         // timing probe: these warps sit the launch out
     } else if (kTimingProbes && warp < 4 && (flags & kFlagNoEpilogue)) {
         // timing probe: these warps sit the launch out
-    } else if (warp >= 6) {
+    } else if (warp >= kFirstSfWarp) {
         // ------------------------------ scale factors: shared memory -> TMEM
+        // kSfSets sets of four warps (one warp per TMEM lane quadrant in each set) take
+        // turns k-tile by k-tile.  One warp needs ~900 cycles per k-tile (two or three
+        // barrier waits, twelve shared-memory loads, the stores, a fence, an arrival);
+        // the MMAs of a k-tile take 520.
+        const uint32_t sf_set = static_cast<uint32_t>(warp - kFirstSfWarp) >> 2;
         // Lane r of the warp serving quadrant q reads row r of each 512-byte atom
         // (16 bytes = the row's scale factors for four 16-k blocks of four 32-row
         // groups) and writes it to TMEM lane 32q + r, four columns per atom.  A
@@ -499,26 +622,45 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
         bool ok = true;
         const bool skip = kTimingProbes && (flags & kFlagSkipSfCopy);
         constexpr int kAtoms = ModeTraits<M>::kHasBHi ? 3 : 2;
-        Tracer trace(kTimingProbes && lane == 0 ? p.trace : nullptr, warp == 6 ? 1 : warp - 3);   // roles 1, 4, 5, 6
+        Tracer trace(kTimingProbes && lane == 0 && sf_set == 0 ? p.trace : nullptr,
+                     warp == kFirstSfWarp ? 1 : warp - kFirstSfWarp + 3);   // roles 1, 4, 5, 6
+        // v holds one k-tile's scale factors in TMEM column order: per 64-k block
+        // [SFA 4 | SFB-lo 4 | SFB-hi 4] words.  The next k-tile is read into it right
+        // after the current one has been handed over, so the loads are off the path
+        // between "ring unit free" and "handed to the MMA warp".
+        constexpr int kWordsPerBlock = TM::kSlotCols;
+        uint32_t v[kKBlocks * kWordsPerBlock];
+        bool loaded = false;
+        auto load_k_tile = [&](uint32_t stage_index, uint32_t phase) -> bool {
+            if (!mbar_wait_warp(smem_u32(&ctl->full[stage_index]), phase, lane, abort_flag, p.status, kStatusSfWait))
+                return false;
+            const uint32_t src = smem_base + stage_index * L::kBytes + lane * 16;
+#pragma unroll
+            for (int kb = 0; kb < kKBlocks; ++kb) {
+                uint32_t* d = v + kb * kWordsPerBlock;
+                ld_shared_v4(src + L::kOffSfA + kb * kSfAtomBytes, d[0], d[1], d[2], d[3]);
+                ld_shared_v4(src + L::kOffSfBLo + kb * kSfAtomBytes, d[4], d[5], d[6], d[7]);
+                if constexpr (kAtoms == 3) ld_shared_v4(src + L::kOffSfBHi + kb * kSfAtomBytes, d[8], d[9], d[10], d[11]);
+            }
+            return true;
+        };
         for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x) {
             const Work w = S::get(p, unit, cursor);
             for (int i = 0; ok && i < w.k_tile_count; ++i) {
-                if (!mbar_wait_warp(smem_u32(&ctl->full[s]), ph, lane, abort_flag, p.status, kStatusSfWait)) {
+                if ((kt % kSfSets) != sf_set) {
+                    // the other set's k-tile: only keep the counters in step
+                    units += kUnitsPerKTile;
+                    buf += kUnitsPerKTile;
+                    if (buf >= static_cast<uint32_t>(TM::kBuffers)) { buf -= TM::kBuffers; ++use; }
+                    ++kt;
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
+                    continue;
+                }
+                if (!loaded && !load_k_tile(s, ph)) {
                     ok = false;
                     break;
                 }
-                trace(1);   // stage landed
-                uint32_t v[kKBlocks][kAtoms][4];
-                const uint32_t src = smem_base + s * L::kBytes + lane * 16;
-#pragma unroll
-                for (int kb = 0; kb < kKBlocks; ++kb) {
-                    ld_shared_v4(src + L::kOffSfA + kb * kSfAtomBytes, v[kb][0][0], v[kb][0][1], v[kb][0][2], v[kb][0][3]);
-                    ld_shared_v4(src + L::kOffSfBLo + kb * kSfAtomBytes, v[kb][1][0], v[kb][1][1], v[kb][1][2],
-                                 v[kb][1][3]);
-                    if constexpr (kAtoms == 3)
-                        ld_shared_v4(src + L::kOffSfBHi + kb * kSfAtomBytes, v[kb][2][0], v[kb][2][1], v[kb][2][2],
-                                     v[kb][2][3]);
-                }
+                trace(1);   // k-tile in registers
 #pragma unroll
                 for (int gr = 0; gr < kKBlocks / TM::kGranule; ++gr, ++units) {
                     // The unit's previous contents were read by the MMAs of k-tile
@@ -526,40 +668,48 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                     // (one tcgen05.commit per k-tile) says when those have retired.
                     if (units >= static_cast<uint32_t>(TM::kBuffers)) {
                         const uint32_t need = (units - TM::kBuffers) / kUnitsPerKTile;
-                        while (ok && retired <= need) {
-                            ok = mbar_wait_warp(smem_u32(&ctl->empty[rs]), rph, lane, abort_flag, p.status,
-                                                kStatusSfWait);
-                            ++retired;
-                            if (++rs == kStages) { rs = 0; rph ^= 1u; }
+                        if (retired <= need) {
+                            // k-tiles retire in issue order (one issuer): waiting for the newest one
+                            // needed covers the older ones; with two issuers every one is waited for
+                            while (kIssuers == 1 && retired < need) {
+                                ++retired;
+                                if (++rs == kStages) { rs = 0; rph ^= 1u; }
+                            }
+                            while (ok && retired <= need) {
+                                ok = mbar_wait_warp(smem_u32(&ctl->empty[rs]), rph, lane, abort_flag, p.status,
+                                                    kStatusSfWait);
+                                ++retired;
+                                if (++rs == kStages) { rs = 0; rph ^= 1u; }
+                            }
+                            if (!ok) break;
+                            tc_fence_after_sync();
                         }
-                        if (!ok) break;
-                        tc_fence_after_sync();
                     }
                     trace(2);   // ring unit free
                     if (!skip || use == 0) {
-#pragma unroll
-                        for (int q = 0; q < TM::kGranule; ++q) {
-                            const int kb = gr * TM::kGranule + q;
-                            const int slot = buf * TM::kGranule + q;
-                            tc_st_x4(tmem_base + quad_lane + TM::sfa_col(slot), v[kb][0][0], v[kb][0][1], v[kb][0][2],
-                                     v[kb][0][3]);
-                            tc_st_x4(tmem_base + quad_lane + TM::sfb_col(slot), v[kb][1][0], v[kb][1][1], v[kb][1][2],
-                                     v[kb][1][3]);
-                            if constexpr (kAtoms == 3)
-                                tc_st_x4(tmem_base + quad_lane + TM::sfb_col(slot) + 4, v[kb][2][0], v[kb][2][1],
-                                         v[kb][2][2], v[kb][2][3]);
+                        // one unit = kGranule blocks = contiguous TMEM columns
+                        const uint32_t dst = tmem_base + quad_lane + TM::sfa_col(buf * TM::kGranule);
+                        const uint32_t* src = v + gr * TM::kGranule * kWordsPerBlock;
+                        constexpr int kUnitWords = TM::kGranule * kWordsPerBlock;   // 24 (N=256 modes) or 32
+                        if constexpr (kUnitWords == 24) {
+                            tc_st_x16(dst, src);
+                            tc_st_x8(dst + 16, src + 16);
+                        } else {
+                            tc_st_x16(dst, src);
+                            tc_st_x16(dst + 16, src + 16);
                         }
-                        tc_wait_st();
                     }
                     if (++buf == TM::kBuffers) { buf = 0; ++use; }
                 }
                 if (!ok) break;
+                if (!skip || use == 0) tc_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->sf_ready[kt & 3u]));
                 trace(3);   // k-tile handed to the MMA warp
                 ++kt;
                 if (++s == kStages) { s = 0; ph ^= 1u; }
+                loaded = false;
             }
         }
     } else if (warp == 5) {
@@ -594,33 +744,37 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
             }
         }
         __syncwarp();
-    } else if (warp == 4) {
-        // ------------------------------ MMA issuer
-        // One thread issues every MMA of the CTA.  Each tcgen05.mma, tcgen05.commit
-        // and mbarrier.try_wait costs that thread about 50 cycles, and four MMAs
-        // occupy the tensor pipe for 520: the loop has room for four MMAs, one wait
-        // and one commit per k-tile and little else.  So: one wait per k-tile (on
-        // the scale factors; their writers waited for the stage's `full` barrier
-        // before reading the stage, which orders the operand bytes before these
-        // MMAs too), one commit per k-tile, 32-bit descriptor words advanced by
-        // constants, counters kept incrementally.
+    } else if (warp == 4 || (kIssuers == 2 && kSfSets == 2 && warp == 6)) {
+        // ------------------------------ MMA issuer(s)
+        // kIssuers threads (on different SM sub-partitions) issue the MMAs, taking
+        // turns k-tile by k-tile.  Each tcgen05.mma, tcgen05.commit and
+        // mbarrier.try_wait costs its thread about 50 cycles; four MMAs occupy the
+        // tensor pipe for 520 cycles, so the loop is kept to the bare minimum.
+        // Per k-tile an issuer does one wait (on the scale factors; their writers
+        // waited for the stage's `full` barrier before reading the stage, which
+        // orders the operand bytes before these MMAs too), four MMAs and one commit.
+        // Accumulation commutes, so with two issuers the streams need no mutual order
+        // except at the start of a tile: the k-tile that clears the accumulator must have
+        // retired before the other issuer adds to it.
         if (lane == 0) {
             using T = ModeTraits<M>;
             constexpr uint32_t kUnitCols = TM::kGranule * TM::kSlotCols;
+            constexpr uint32_t kUnitsPerKTile = kKBlocks / TM::kGranule;
+            const uint32_t me = (warp == 4) ? 0u : 1u;
             const uint32_t desc_lo_base = smem_desc_lo(smem_base + L::kOffA);
             const uint32_t sf_ready_bar = smem_u32(&ctl->sf_ready[0]);
             const uint32_t empty_bar = smem_u32(&ctl->empty[0]);
             const uint32_t sf_base = tmem_base + TM::kSfBase;
-            uint32_t s = 0, a_lo = desc_lo_base;   // stage and the low word of its A descriptor
-            uint32_t kt = 0;                       // running k-tile count
-            uint32_t buf = 0;                      // scale-factor ring unit
+            uint32_t s = 0, s_use = 0, a_lo = desc_lo_base;   // stage, how often it has been used, its A descriptor
+            uint32_t kt = 0;                                   // running k-tile count
+            uint32_t buf = 0;                                  // scale-factor ring unit of the k-tile's first half
             int cursor = 0, it = 0;
             bool failed = false;
             const int mma_blocks = (kTimingProbes && (flags & kFlagSkipMma)) ? 1 : kKBlocks;
             const bool no_sf = kTimingProbes && (flags & kFlagNoSfWarps);
             const bool no_epi = kTimingProbes && (flags & kFlagNoEpilogue);
-            Tracer trace(kTimingProbes ? p.trace : nullptr, 0);
-            for (int unit = blockIdx.x; unit < total; unit += gridDim.x, ++it) {
+            Tracer trace(kTimingProbes && me == 0 ? p.trace : nullptr, 0);
+            for (int unit = blockIdx.x; unit < total && !failed; unit += gridDim.x, ++it) {
                 const Work w = S::get(p, unit, cursor);
                 if (it > 0 && !no_epi) {
                     const int r = it - 1;   // wait for hand-back number r
@@ -634,42 +788,59 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                 trace(9);   // accumulator buffer available
                 const uint32_t acc_addr = tmem_base + (it & 1) * TM::kAccStride;
                 const int k_tiles = w.k_tile_count;
+                // the tile's first k-tile clears the accumulator; if the other issuer owns it,
+                // wait until it has retired (its stage's `empty` barrier) before adding anything
+                const bool first_is_mine = (kt % kIssuers) == me;
+                const uint32_t first_empty = empty_bar + s * 8, first_parity = s_use & 1u;
+                bool first_done = first_is_mine;
 #pragma unroll 1
                 for (int i = 0; i < k_tiles; ++i) {
-                    const uint32_t bar = no_sf ? smem_u32(&ctl->full[s]) : sf_ready_bar + (kt & 3u) * 8u;
-                    const uint32_t parity = no_sf ? (kt / kStages) & 1u : (kt >> 2) & 1u;
-                    if (!mbar_wait(bar, parity, abort_flag, p.status, kStatusMmaWaitFull)) {
-                        failed = true;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    trace(1);   // k-tile ready
+                    if (kIssuers == 1 || (kt % kIssuers) == me) {
+                        if (kIssuers > 1 && !first_done) {
+                            if (!mbar_wait(first_empty, first_parity, abort_flag, p.status, kStatusMmaWaitAcc)) {
+                                failed = true;
+                                break;
+                            }
+                            first_done = true;
+                        }
+                        const uint32_t bar = no_sf ? smem_u32(&ctl->full[s]) : sf_ready_bar + (kt & 3u) * 8u;
+                        const uint32_t parity = no_sf ? s_use & 1u : (kt >> 2) & 1u;
+                        if (!mbar_wait(bar, parity, abort_flag, p.status, kStatusMmaWaitFull)) {
+                            failed = true;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        trace(1);   // k-tile ready
+                        uint32_t b = buf;
 #pragma unroll
-                    for (int kb = 0; kb < kKBlocks; ++kb) {
-                        if (kb > 0 && kb % TM::kGranule == 0) buf = (buf + 1 == TM::kBuffers) ? 0u : buf + 1;
-                        if (kTimingProbes && kb >= mma_blocks) continue;
-                        const uint32_t sfa = sf_base + buf * kUnitCols + (kb % TM::kGranule) * TM::kSlotCols;
-                        tc_mma_mxf4nvf4_lo(acc_addr, a_lo + 2 * kb, a_lo + (L::kOffBLo >> 4) + 2 * kb,
-                                           idesc_mxf4nvf4(128, T::kMmaN), sfa, sfa + 4, (kb > 0 || i > 0) ? 1u : 0u);
+                        for (int kb = 0; kb < kKBlocks; ++kb) {
+                            if (kb > 0 && kb % TM::kGranule == 0) b = (b + 1 == TM::kBuffers) ? 0u : b + 1;
+                            if (kTimingProbes && kb >= mma_blocks) continue;
+                            const uint32_t sfa = sf_base + b * kUnitCols + (kb % TM::kGranule) * TM::kSlotCols;
+                            tc_mma_mxf4nvf4_lo(acc_addr, a_lo + 2 * kb, a_lo + (L::kOffBLo >> 4) + 2 * kb,
+                                               idesc_mxf4nvf4(128, T::kMmaN), sfa, sfa + 4,
+                                               (kb > 0 || i > 0) ? 1u : 0u);
+                        }
+                        // one commit per k-tile: frees the stage for the producer and tells the
+                        // scale-factor warps that the ring units this k-tile read are reusable
+                        tc_commit(empty_bar + s * 8);
                     }
-                    buf = (buf + 1 == TM::kBuffers) ? 0u : buf + 1;
-                    // one commit per k-tile: frees the stage for the producer and tells the
-                    // scale-factor warps that the ring units this k-tile read are reusable
-                    tc_commit(empty_bar + s * 8);
                     ++kt;
+                    buf += kUnitsPerKTile;
+                    if (buf >= static_cast<uint32_t>(TM::kBuffers)) buf -= TM::kBuffers;
                     ++s;
                     a_lo += L::kBytes >> 4;
-                    if (s == kStages) { s = 0; a_lo = desc_lo_base; }
+                    if (s == kStages) { s = 0; a_lo = desc_lo_base; ++s_use; }
                 }
                 if (failed) break;
-                tc_commit(smem_u32(&ctl->acc_full[it & 1]));
+                tc_commit(smem_u32(&ctl->acc_full[it & 1]));   // arrives once this issuer's MMAs of the tile retire
             }
             // drain: every MMA issued above must retire before TMEM is freed
-            tc_commit(smem_u32(&ctl->aux));
-            mbar_wait(smem_u32(&ctl->aux), 0, abort_flag, p.status, kStatusMmaWaitAcc);
+            tc_commit(smem_u32(&ctl->aux[me]));
+            mbar_wait(smem_u32(&ctl->aux[me]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
         }
         __syncwarp();
-    } else {
+    } else if (warp < 4) {
         // ------------------------------ epilogue warps 0-3
         int cursor = 0, it = 0;
         bool ok = true;
@@ -690,7 +861,14 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
             tc_fence_after_sync();
             trace(1);   // accumulator complete
             const bool store = !(kTimingProbes && (flags & kFlagSkipStores));
-            if (it & 1)
+            bool split = false;
+            if constexpr (M == Mode::Dual) split = p.k_splits > 1;
+            if (split) {
+                if constexpr (M == Mode::Dual) {
+                    ok = (it & 1) ? epilogue_tile_splitk<1>(p, w, tmem_base, warp, lane, release_bar, abort_flag)
+                                  : epilogue_tile_splitk<0>(p, w, tmem_base, warp, lane, release_bar, abort_flag);
+                }
+            } else if (it & 1)
                 epilogue_tile<M, 1>(w, tmem_base, warp, lane, release_bar, store);
             else
                 epilogue_tile<M, 0>(w, tmem_base, warp, lane, release_bar, store);

@@ -112,6 +112,19 @@ def test_grouped_argument_errors(pkg):
     assert _grouped(lib, [(0, 128, 256), (0, 256, 512)], null_group=1) == 0
 
 
+def test_split_k_workspace_size(pkg):
+    lib = pkg._lib.load()
+    f = lib.b200_dual_splitk_workspace_bytes
+    assert f(8192, 14336, 4096, 1) == 0                       # 7168 tiles: never split
+    assert f(512, 4096, 7168, 1) == 0                         # 128 tiles: more than half of the 148 SMs already
+    tile = 128 * 256 * 4
+    assert f(1536, 512, 7168, 1) == 48 * 32 + 48 * 3 * tile       # 48 tiles, 28 k-tiles -> 3 pieces
+    assert f(256, 4096, 7168, 1) == 64 * 32 + 64 * 2 * tile       # 64 tiles, 28 k-tiles -> 2 pieces
+    assert f(256, 3072, 4096, 1) == 48 * 32 + 48 * 3 * tile       # 48 tiles, 16 k-tiles -> 3 pieces
+    assert f(128, 128, 256, 1) == 0                           # one k-tile cannot be cut
+    assert f(100, 128, 256, 1) == 0 and f(128, 128, 0, 1) == 0
+
+
 def test_workspace_size(pkg):
     lib = pkg._lib.load()
     assert lib.b200_grouped_workspace_bytes(0) == 0
