@@ -12,7 +12,7 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200nvfp4.so")
 
-VARIANT_AUTO, VARIANT_PERSISTENT, VARIANT_SERIAL, VARIANT_SERIAL_2MMA, VARIANT_SPLITK = 0, 1, 2, 3, 4
+VARIANT_AUTO, VARIANT_PERSISTENT, VARIANT_SERIAL, VARIANT_SERIAL_2MMA, VARIANT_SPLITK, VARIANT_PAIR = 0, 1, 2, 3, 4, 5
 
 E_NULL, E_SHAPE, E_ALIGN, E_WORKSPACE, E_VARIANT, E_DRIVER, E_LIMIT = -1, -2, -3, -4, -5, -6, -7
 

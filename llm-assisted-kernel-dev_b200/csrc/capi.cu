@@ -11,6 +11,7 @@
 
 #include "../../include/b200_nvfp4.h"
 #include "nvfp4_gemm_kernels.cuh"
+#include "nvfp4_dual_pair_kernel.cuh"
 
 namespace b200 {
 namespace {
@@ -125,6 +126,7 @@ int device_state(int device, DeviceState** out) {
                               smem_bytes_persistent<Mode::Group128, kG128Stages>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Group256, kG256Stages>,
                               smem_bytes_persistent<Mode::Group256, kG256Stages>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_dual_gemm_pair, kPairSmemBytes))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Dual>, smem_bytes_serial<Mode::Dual>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group128>, smem_bytes_serial<Mode::Group128>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group256>, smem_bytes_serial<Mode::Group256>()))) return rc;
@@ -214,6 +216,29 @@ int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStr
     return 0;
 }
 
+// CTA pairs: clusters of two CTAs, one pair per TPC, each pair walks pair tiles.
+int launch_pair(const DenseProblem& prob, int sm_count, int flags, cudaStream_t stream) {
+    const int pair_tiles = (prob.m_tiles / 2) * prob.n_tiles * prob.batches;
+    int pairs = sm_count / 2;
+    if (pairs > pair_tiles) pairs = pair_tiles;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(320, 1, 1);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_dual_gemm_pair, prob, flags));
+    ++g_launches;
+    return 0;
+}
+
 template <Mode M, typename P> int launch_serial(const P& prob, int units, int two_mma, cudaStream_t stream) {
     nvfp4_gemm_serial<M><<<units, 128, smem_bytes_serial<M>(), stream>>>(prob, two_mma);
     B200_CUDA(cudaGetLastError());
@@ -251,7 +276,8 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     int rc = validate_dual(a, b1, b2, sfa, sfb1, sfb2, c, m, n, k, l, ldc, c_batch, b_batch_bytes, sfb_batch_bytes);
     if (rc) return rc;
     const bool probe = variant >= B200_VARIANT_PROBE_BASE && variant < B200_VARIANT_PROBE_BASE + 256;
-    if (!probe && (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_SPLITK))
+    const bool pair_probe = variant >= B200_VARIANT_PROBE_BASE + 300 && variant < B200_VARIANT_PROBE_BASE + 556;
+    if (!probe && !pair_probe && (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_PAIR))
         return fail(B200_E_VARIANT, "dual gemm: unknown variant %d", variant);
 
     std::lock_guard<std::mutex> lock(g_mutex);
@@ -322,6 +348,12 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     }
     if (p.k_splits > 1)
         return launch_persistent<Mode::Dual, kDualStages>(p, p.total_tiles * p.k_splits, st->sm_count, 0, s);
+    if (pair_probe && p.m_tiles % 2 == 0)
+        return launch_pair(p, st->sm_count, variant - B200_VARIANT_PROBE_BASE - 300, s);
+    if (variant == B200_VARIANT_PAIR) {
+        if (p.m_tiles % 2) return fail(B200_E_SHAPE, "dual gemm: CTA pairs need m to be a multiple of 256 (m=%d)", m);
+        return launch_pair(p, st->sm_count, 0, s);
+    }
     switch (variant) {
         case B200_VARIANT_SERIAL:
             return launch_serial<Mode::Dual>(p, p.total_tiles, 0, s);

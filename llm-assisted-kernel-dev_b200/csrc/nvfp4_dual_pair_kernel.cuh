@@ -1,0 +1,304 @@
+// Dual GEMM on CTA pairs (tcgen05 cta_group::2): two CTAs on the two SMs of a TPC
+// share one 256 x 128 output tile of C = silu(A.B1^T) * (A.B2^T).
+//
+// Why: in the one-CTA kernel a 128x256x64 MMA reads 12 KB of operands from shared
+// memory (A 4 KB + merged B 8 KB) every 130 cycles, the TMA fills add 54 KB per
+// k-tile and the scale-factor warps read another 24 KB: about 126 KB per k-tile on
+// a 128 B/clk shared memory is ~1000 cycles, twice the 520 the four MMAs need.  In
+// a pair each CTA holds its own 128 rows of A and *half* of the merged B (CTA 0 the
+// B1 tile, CTA 1 the B2 tile): per CTA the MMAs read 32 KB per k-tile, the TMA
+// fills 38 KB, the scale-factor warps 24 KB.
+//
+// Division of labour (same ten warps per CTA as the one-CTA kernel):
+//   producer          each CTA loads its own A tile, its B tile, its SFA chunk and
+//                     both SFB chunks; signals its own `full` barrier
+//   scale factors     each CTA's four warps fill their own TMEM (SFA of the CTA's
+//                     rows, SFB of all 256 merged-B rows); they arrive on the
+//                     *first* CTA's hand-over barrier (eight arrivals per k-tile)
+//   MMA               one thread of the first CTA issues every MMA for the pair;
+//                     it commits to both CTAs' `empty` and `acc_full` barriers
+//   epilogue          each CTA drains its own 128 accumulator rows; both hand the
+//                     buffer back on the first CTA's `acc_release` barrier
+// No load carries a cluster-multicast qualifier; the partner is only ever signalled
+// through mbarrier arrivals.
+#pragma once
+
+#include "nvfp4_gemm_kernels.cuh"
+
+namespace b200 {
+
+struct PairStage {
+    static constexpr uint32_t kOffA = 0;
+    static constexpr uint32_t kOffB = kOperandTileBytes;                 // this CTA's half of merged B
+    static constexpr uint32_t kOffSfA = 2 * kOperandTileBytes;
+    static constexpr uint32_t kOffSfB1 = kOffSfA + kSfChunkBytes;
+    static constexpr uint32_t kOffSfB2 = kOffSfB1 + kSfChunkBytes;
+    static constexpr uint32_t kBytes = kOffSfB2 + kSfChunkBytes;        // 38 KiB, multiple of 1024
+};
+constexpr int kPairStages = 5;
+constexpr uint32_t kPairSmemBytes = 1024u + kPairStages * PairStage::kBytes + sizeof(ControlBlock);
+constexpr uint32_t kStatusPairWait = 0x80;
+
+// Work of one CTA of the pair for pair-tile `tile`: rows of A/C are those of the
+// CTA's rank, the B tile is B1 for rank 0 and B2 for rank 1.
+__device__ __forceinline__ Work pair_work(const DenseProblem& p, int tile, uint32_t rank) {
+    const int m_pairs = p.m_tiles / 2;
+    const int m_pair = tile % m_pairs;
+    const int t = tile / m_pairs;
+    const int n_blk = t % p.n_tiles;
+    const int b = t / p.n_tiles;
+    const int m_blk = 2 * m_pair + static_cast<int>(rank);
+    Work w;
+    w.map_a = &p.map_a;
+    w.map_blo = rank == 0 ? static_cast<const void*>(&p.map_b1) : static_cast<const void*>(&p.map_b2);
+    w.map_bhi = w.map_blo;
+    w.a_row = m_blk * kTileM;
+    w.blo_row = w.bhi_row = n_blk * 128;
+    w.batch = b;
+    const long long sf_row = static_cast<long long>(p.sf_k_atoms) * kSfAtomBytes;
+    w.sfa = p.sfa + b * p.sfa_batch + m_blk * sf_row;
+    w.sfblo = p.sfb1 + b * p.sfb_batch + n_blk * sf_row;
+    w.sfbhi = p.sfb2 + b * p.sfb_batch + n_blk * sf_row;
+    w.ldc = p.ldc;
+    w.c = p.c + b * p.c_batch + static_cast<long long>(m_blk) * kTileM * p.ldc + n_blk * 128;
+    w.rows_valid = kTileM;
+    w.cols_valid = 128;
+    w.k_tile_begin = 0;
+    w.k_tile_count = p.k_tiles;
+    w.group = 0;
+    w.tile = tile;
+    w.split = 0;
+    return w;
+}
+
+__global__ void __launch_bounds__(320, 1)
+nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
+    using TM = TmemMap<Mode::Dual>;
+    using T = ModeTraits<Mode::Dual>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    ControlBlock* ctl = reinterpret_cast<ControlBlock*>(smem_raw + (smem_base - smem_u32(smem_raw)) +
+                                                        kPairStages * PairStage::kBytes);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();          // 0: issues the MMAs, 1: partner
+    const int pair = blockIdx.x >> 1;
+    const int pairs = gridDim.x >> 1;
+    const int total = (p.m_tiles / 2) * p.n_tiles * p.batches;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairStages; ++s) {
+            mbar_init(smem_u32(&ctl->full[s]), 1);
+            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl->acc_full[b]), 1);
+            mbar_init(smem_u32(&ctl->acc_release[b]), 8);   // four epilogue warps in each CTA (used in CTA 0)
+        }
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->sf_ready[i]), 8);   // used in CTA 0
+        mbar_init(smem_u32(&ctl->aux[0]), 1);
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 4) {
+        tmem_alloc_pair(smem_u32(&ctl->tmem_base), kTmemColumns);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_arrive();      // the partner's barriers exist before anybody signals them
+    cluster_wait();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+    if (warp >= 6) {
+        // ------------------------------ scale factors: own shared memory -> own TMEM
+        const uint32_t quad_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        constexpr uint32_t kUnitsPerKTile = kKBlocks / TM::kGranule;
+        uint32_t s = 0, ph = 0, kt = 0, buf = 0, units = 0, retired = 0, rs = 0, rph = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < total; tile += pairs) {
+            for (int i = 0; ok && i < p.k_tiles; ++i) {
+                if (!mbar_wait_warp(smem_u32(&ctl->full[s]), ph, lane, abort_flag, p.status, kStatusSfWait)) {
+                    ok = false;
+                    break;
+                }
+                uint32_t v[kKBlocks * 12];
+                const uint32_t src = smem_base + s * PairStage::kBytes + lane * 16;
+#pragma unroll
+                for (int kb = 0; kb < kKBlocks; ++kb) {
+                    uint32_t* d = v + kb * 12;
+                    ld_shared_v4(src + PairStage::kOffSfA + kb * kSfAtomBytes, d[0], d[1], d[2], d[3]);
+                    ld_shared_v4(src + PairStage::kOffSfB1 + kb * kSfAtomBytes, d[4], d[5], d[6], d[7]);
+                    ld_shared_v4(src + PairStage::kOffSfB2 + kb * kSfAtomBytes, d[8], d[9], d[10], d[11]);
+                }
+                // ring units of this k-tile were last read by k-tile (units + 1 - kBuffers) / 2
+                const uint32_t last_unit = units + kUnitsPerKTile - 1;
+                const bool probe_skip = (flags & kFlagSkipSfCopy) && kt >= 2;   // timing probe
+                if (!probe_skip && last_unit >= static_cast<uint32_t>(TM::kBuffers)) {
+                    const uint32_t need = (last_unit - TM::kBuffers) / kUnitsPerKTile;
+                    if (retired <= need) {
+                        while (retired < need) {
+                            ++retired;
+                            if (++rs == kPairStages) { rs = 0; rph ^= 1u; }
+                        }
+                        // arrived on by the first CTA's tcgen05.commit: cluster-scope acquire
+                        uint32_t good = 1;
+                        if (lane == 0)
+                            good = mbar_wait_cluster(smem_u32(&ctl->empty[rs]), rph, abort_flag, p.status, kStatusSfWait);
+                        ok = __shfl_sync(0xffffffffu, good, 0) != 0;
+                        ++retired;
+                        if (++rs == kPairStages) { rs = 0; rph ^= 1u; }
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                    }
+                }
+                if (!probe_skip) {
+#pragma unroll
+                    for (int gr = 0; gr < static_cast<int>(kUnitsPerKTile); ++gr) {
+                        uint32_t b = buf + gr;
+                        if (b >= static_cast<uint32_t>(TM::kBuffers)) b -= TM::kBuffers;
+                        const uint32_t dst = tmem_base + quad_lane + TM::sfa_col(b * TM::kGranule);
+                        tc_st_x16(dst, v + gr * 24);
+                        tc_st_x8(dst + 16, v + gr * 24 + 16);
+                    }
+                    tc_wait_st();
+                }
+                units += kUnitsPerKTile;
+                buf += kUnitsPerKTile;
+                if (buf >= static_cast<uint32_t>(TM::kBuffers)) buf -= TM::kBuffers;
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->sf_ready[kt & 3u]), 0));
+                ++kt;
+                if (++s == kPairStages) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ TMA producer (each CTA for itself)
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < total; tile += pairs) {
+                const Work w = pair_work(p, tile, rank);
+                for (int i = 0; i < p.k_tiles; ++i) {
+                    if (!mbar_wait_cluster(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
+                                           kStatusProducerWait)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t stage = smem_base + s * PairStage::kBytes;
+                    const uint32_t bar = smem_u32(&ctl->full[s]);
+                    if (flags & kFlagSkipLoads) {   // timing probe
+                        mbar_arrive(bar);
+                        if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                        continue;
+                    }
+                    mbar_arrive_expect_tx(bar, PairStage::kBytes);
+                    tma_load_3d(stage + PairStage::kOffA, w.map_a, bar, i * 128, w.a_row, w.batch);
+                    tma_load_3d(stage + PairStage::kOffB, w.map_blo, bar, i * 128, w.blo_row, w.batch);
+                    const long long sf_off = static_cast<long long>(i) * kSfChunkBytes;
+                    bulk_load(stage + PairStage::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
+                    bulk_load(stage + PairStage::kOffSfB1, w.sfblo + sf_off, kSfChunkBytes, bar);
+                    bulk_load(stage + PairStage::kOffSfB2, w.sfbhi + sf_off, kSfChunkBytes, bar);
+                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                }
+            }
+            if (!ok)
+                for (int i = 0; i < 64; ++i) __nanosleep(2000);   // error path: let copies in flight land
+        }
+        __syncwarp();
+    } else if (warp == 4) {
+        // ------------------------------ MMA issuer (first CTA of the pair only)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t kUnitCols = TM::kGranule * TM::kSlotCols;
+            const uint32_t desc_lo_base = smem_desc_lo(smem_base + PairStage::kOffA);
+            const uint32_t sf_ready_bar = smem_u32(&ctl->sf_ready[0]);
+            const uint32_t empty_mine = smem_u32(&ctl->empty[0]);
+            const uint32_t empty_peer = map_to_cta(empty_mine, 1);
+            const uint32_t sf_base = tmem_base + TM::kSfBase;
+            uint32_t s = 0, a_lo = desc_lo_base, kt = 0, buf = 0;
+            int it = 0;
+            bool failed = false;
+            for (int tile = pair; tile < total && !failed; tile += pairs, ++it) {
+                if (it > 0) {
+                    const int r = it - 1;
+                    if (!mbar_wait_cluster(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
+                                           kStatusMmaWaitAcc)) {
+                        failed = true;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                }
+                const uint32_t acc_addr = tmem_base + (it & 1) * TM::kAccStride;
+#pragma unroll 1
+                for (int i = 0; i < p.k_tiles; ++i) {
+                    // eight arrivals: both CTAs' scale factors are in TMEM; the arriving warps
+                    // waited for their CTA's operands first
+                    if (!mbar_wait_cluster(sf_ready_bar + (kt & 3u) * 8u, (kt >> 2) & 1u, abort_flag, p.status,
+                                           kStatusMmaWaitFull)) {
+                        failed = true;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    uint32_t b = buf;
+#pragma unroll
+                    for (int kb = 0; kb < kKBlocks; ++kb) {
+                        if (kb > 0 && kb % TM::kGranule == 0) b = (b + 1 == TM::kBuffers) ? 0u : b + 1;
+                        const uint32_t sfa = sf_base + b * kUnitCols + (kb % TM::kGranule) * TM::kSlotCols;
+                        tc_mma_mxf4nvf4_pair_lo(acc_addr, a_lo + 2 * kb, a_lo + (PairStage::kOffB >> 4) + 2 * kb,
+                                                idesc_mxf4nvf4(256, T::kMmaN), sfa, sfa + 4,
+                                                (kb > 0 || i > 0) ? 1u : 0u);
+                    }
+                    tc_commit_pair(empty_mine + s * 8);
+                    tc_commit_pair(empty_peer + s * 8);
+                    ++kt;
+                    buf += kKBlocks / TM::kGranule;
+                    if (buf >= static_cast<uint32_t>(TM::kBuffers)) buf -= TM::kBuffers;
+                    ++s;
+                    a_lo += PairStage::kBytes >> 4;
+                    if (s == kPairStages) { s = 0; a_lo = desc_lo_base; }
+                }
+                if (failed) break;
+                tc_commit_pair(smem_u32(&ctl->acc_full[it & 1]));
+                tc_commit_pair(map_to_cta(smem_u32(&ctl->acc_full[it & 1]), 1));
+            }
+            tc_commit_pair(smem_u32(&ctl->aux[0]));
+            mbar_wait(smem_u32(&ctl->aux[0]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
+        }
+        __syncwarp();
+    } else if (warp < 4) {
+        // ------------------------------ epilogue (each CTA its own 128 rows)
+        int it = 0;
+        for (int tile = pair; tile < total; tile += pairs, ++it) {
+            const Work w = pair_work(p, tile, rank);
+            const uint32_t release_bar = map_to_cta(smem_u32(&ctl->acc_release[it & 1]), 0);
+            uint32_t good = 1;
+            if (lane == 0)
+                good = mbar_wait_cluster(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
+                                         kStatusEpilogueWait);
+            if (__shfl_sync(0xffffffffu, good, 0) == 0) break;
+            tc_fence_after_sync();
+            const bool store = !(flags & kFlagSkipStores);   // timing probe
+            if (it & 1)
+                epilogue_tile<Mode::Dual, 1, true>(w, tmem_base, warp, lane, release_bar, store);
+            else
+                epilogue_tile<Mode::Dual, 0, true>(w, tmem_base, warp, lane, release_bar, store);
+            tc_fence_before_sync();
+        }
+    }
+    // Nobody leaves while the partner may still signal its barriers or while MMAs
+    // issued by the first CTA still run on this SM.
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 4) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, kTmemColumns);
+    }
+}
+
+}  // namespace b200

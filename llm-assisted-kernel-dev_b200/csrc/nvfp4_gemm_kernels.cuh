@@ -381,7 +381,7 @@ __device__ __forceinline__ void store_chunk(__half* row_ptr, int chunk, const ui
 // other product of the dual GEMM) are not shared and are read later.
 //   buffer 0 (columns 0-255):   shared = its columns 160-255
 //   buffer 1 (columns 160-415): shared = its columns 0-95
-template <Mode M, int kBuf>
+template <Mode M, int kBuf, bool kReleaseInCluster = false>
 __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base, int quad, int lane,
                                               uint32_t release_bar, bool store = true) {
     using T = ModeTraits<M>;
@@ -401,7 +401,10 @@ __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base,
         tc_wait_ld();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(release_bar);
+        if (lane == 0) {
+            if constexpr (kReleaseInCluster) mbar_arrive_cluster(release_bar);   // barrier of the pair's first CTA
+            else mbar_arrive(release_bar);
+        }
     }
     // Which buffer-relative 16-column group feeds x (and y) of output chunk c,
     // and whether that group sits in `early`.

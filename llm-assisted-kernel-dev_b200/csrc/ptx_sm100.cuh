@@ -129,6 +129,62 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// ---------------------------------------------------------------------------
+// Thread-block clusters (CTA pairs)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// Arrive on an mbarrier that lives in any CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// try_wait that also acquires arrivals made by the other CTA of the pair.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t* status, uint32_t code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitTimeoutCycles) {
+            *abort_flag = 1u;
+            atomicOr(status, code);
+            return false;
+        }
+    }
+}
+
 // Warp-wide bounded wait: lane 0 polls, the outcome is broadcast.  Every polling
 // lane is a separate access to the barrier, and barrier traffic from waiting
 // warps slows down the (single) thread that issues the MMAs on the same SM.
@@ -187,6 +243,20 @@ __device__ __forceinline__ void tmem_relinquish() {
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t columns) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns)
+                 : "memory");
+}
+
+// CTA-pair variants: a warp with the same index in both CTAs executes alloc / dealloc.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_slot, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_slot),
+                 "r"(columns)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t base, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns)
                  : "memory");
 }
 
@@ -275,6 +345,32 @@ __device__ __forceinline__ void tc_mma_mxf4nvf4_lo(uint32_t tmem_d, uint32_t ade
         ::"r"(tmem_d), "r"(adesc_lo), "r"(bdesc_lo), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb),
         "r"(kDescHiSw128)
         : "memory");
+}
+
+// The same MMA across a CTA pair (M = 256: each CTA contributes its 128 rows of A
+// and its half of B's rows from the same shared-memory offsets, and receives its
+// 128 rows of D in its own TMEM).  Issued by one thread of the pair's first CTA.
+__device__ __forceinline__ void tc_mma_mxf4nvf4_pair_lo(uint32_t tmem_d, uint32_t adesc_lo, uint32_t bdesc_lo,
+                                                        uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %7};\n\t"
+        "mov.b64 db, {%2, %7};\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], da, db, %3, [%5], [%6], p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "r"(adesc_lo), "r"(bdesc_lo), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb),
+        "r"(kDescHiSw128)
+        : "memory");
+}
+// Arrive on an mbarrier (cluster address: this CTA's or the partner's) once every
+// MMA the pair has been given so far by this thread is done.
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
+                 : "memory");
 }
 
 // mbarrier arrive once every tcgen05 op issued so far by this thread is done.

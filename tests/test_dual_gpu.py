@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 TOL_NORTH_STAR = 1e-2
 TOL_REFERENCE = 1e-3
 
-V_AUTO, V_PERSISTENT, V_SERIAL, V_SERIAL_2MMA, V_SPLITK = 0, 1, 2, 3, 4
+V_AUTO, V_PERSISTENT, V_SERIAL, V_SERIAL_2MMA, V_SPLITK, V_PAIR = 0, 1, 2, 3, 4, 5
 
 
 def _run(pkg, data, variant):
@@ -86,6 +86,26 @@ def test_split_k_shapes(pkg, oracle, m, n, k, variant):
 def test_split_k_with_overflowing_distribution(pkg, oracle):
     data = pkg.inputs.generate_input(256, 2048, 7168, 1, 5, dist="uniform16", device="cuda")
     _check(oracle, data, _run(pkg, data, V_SPLITK), TOL_NORTH_STAR)
+
+
+# CTA pairs (2-SM MMA, 256-row tiles): one pair tile, several k-tiles, several tiles per pair, batches
+@pytest.mark.parametrize("m,n,k,l", [(256, 128, 256, 1), (256, 256, 2560, 1), (512, 384, 512, 2), (2048, 1024, 1536, 1),
+                                     (8192, 3072, 256, 1), (1536, 512, 7168, 1)])
+@pytest.mark.parametrize("dist,tol", [("reference", TOL_REFERENCE), ("uniform16", TOL_NORTH_STAR)])
+def test_cta_pair_variant(pkg, oracle, m, n, k, l, dist, tol):
+    data = pkg.inputs.generate_input(m, n, k, l, 3, dist=dist, device="cuda")
+    out = _run(pkg, data, V_PAIR)
+    _check(oracle, data, out, tol)
+    one_cta = _run(pkg, data, V_PERSISTENT).clone()
+    again = _run(pkg, data, V_PAIR)
+    # same MMAs in the same k order: the pair kernel reproduces the one-CTA kernel bit for bit
+    assert torch.equal(again.view(torch.int16), one_cta.view(torch.int16))
+
+
+def test_cta_pair_needs_even_row_tiles(pkg):
+    data = pkg.inputs.generate_input(384, 128, 256, 1, 0, device="cuda")
+    with pytest.raises(ValueError, match="256"):
+        pkg.dual_gemm.custom_kernel(data, variant=V_PAIR)
 
 
 def test_known_answer_all_ones_overflows_to_inf(pkg):
