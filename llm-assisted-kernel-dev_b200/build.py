@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200nvfp4.so")
 SOURCES = ["capi.cu"]
-HEADERS = ["ptx_sm100.cuh", "nvfp4_gemm_kernels.cuh", os.path.join("..", "..", "include", "b200_nvfp4.h")]
+PUBLIC_HEADER = os.path.join(HERE, "..", "include", "b200_nvfp4.h")
 
 
 def _nvcc() -> str:
@@ -31,7 +31,7 @@ def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS] + [os.path.abspath(__file__)]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [PUBLIC_HEADER, os.path.abspath(__file__)]
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 

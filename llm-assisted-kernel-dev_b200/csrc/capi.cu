@@ -323,7 +323,7 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     p.k_splits = 1;
     p.status = status ? status : st->status;
     // timing probes: an optional 8 x 1024 x 8-byte event log for CTA 0
-    p.trace = (probe && workspace && workspace_bytes >= 8 * 1024 * sizeof(unsigned long long))
+    p.trace = ((probe || pair_probe) && workspace && workspace_bytes >= 8 * 1024 * sizeof(unsigned long long))
                   ? static_cast<unsigned long long*>(workspace) : nullptr;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);

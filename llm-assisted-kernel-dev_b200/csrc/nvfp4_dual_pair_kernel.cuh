@@ -95,7 +95,9 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             mbar_init(smem_u32(&ctl->acc_full[b]), 1);
             mbar_init(smem_u32(&ctl->acc_release[b]), 8);   // four epilogue warps in each CTA (used in CTA 0)
         }
-        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->sf_ready[i]), 8);   // used in CTA 0
+        // one hand-over barrier per stage: a slot is reused only after the MMA thread
+        // passed its previous use (the stage had to be freed in between); used in CTA 0
+        for (int i = 0; i < kPairStages; ++i) mbar_init(smem_u32(&ctl->sf_ready[i]), 8);
         mbar_init(smem_u32(&ctl->aux[0]), 1);
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -119,12 +121,15 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
         constexpr uint32_t kUnitsPerKTile = kKBlocks / TM::kGranule;
         uint32_t s = 0, ph = 0, kt = 0, buf = 0, units = 0, retired = 0, rs = 0, rph = 0;
         bool ok = true;
+        Tracer trace(lane == 0 && blockIdx.x < 2 && (rank == 0 || warp == 6 || warp == 9) ? p.trace : nullptr,
+                     rank == 0 ? warp - 5 : (warp == 6 ? 5 : 6), rank);
         for (int tile = pair; ok && tile < total; tile += pairs) {
             for (int i = 0; ok && i < p.k_tiles; ++i) {
-                if (!mbar_wait_warp(smem_u32(&ctl->full[s]), ph, lane, abort_flag, p.status, kStatusSfWait)) {
+                if (!mbar_wait<true>(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusSfWait)) {
                     ok = false;
                     break;
                 }
+                trace(1);   // operands landed
                 uint32_t v[kKBlocks * 12];
                 const uint32_t src = smem_base + s * PairStage::kBytes + lane * 16;
 #pragma unroll
@@ -144,17 +149,15 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
                             ++retired;
                             if (++rs == kPairStages) { rs = 0; rph ^= 1u; }
                         }
-                        // arrived on by the first CTA's tcgen05.commit: cluster-scope acquire
-                        uint32_t good = 1;
-                        if (lane == 0)
-                            good = mbar_wait_cluster(smem_u32(&ctl->empty[rs]), rph, abort_flag, p.status, kStatusSfWait);
-                        ok = __shfl_sync(0xffffffffu, good, 0) != 0;
+                        // arrived on by the first CTA's tcgen05.commit
+                        ok = mbar_wait<false>(smem_u32(&ctl->empty[rs]), rph, abort_flag, p.status, kStatusSfWait);
                         ++retired;
                         if (++rs == kPairStages) { rs = 0; rph ^= 1u; }
                         if (!ok) break;
                         tc_fence_after_sync();
                     }
                 }
+                trace(2);   // ring units free
                 if (!probe_skip) {
 #pragma unroll
                     for (int gr = 0; gr < static_cast<int>(kUnitsPerKTile); ++gr) {
@@ -171,7 +174,8 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
                 if (buf >= static_cast<uint32_t>(TM::kBuffers)) buf -= TM::kBuffers;
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->sf_ready[kt & 3u]), 0));
+                if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ctl->sf_ready[s]), 0));
+                trace(3);   // handed to the MMA thread
                 ++kt;
                 if (++s == kPairStages) { s = 0; ph ^= 1u; }
             }
@@ -181,14 +185,16 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
+            Tracer trace(nullptr, 0);
             for (int tile = pair; ok && tile < total; tile += pairs) {
                 const Work w = pair_work(p, tile, rank);
                 for (int i = 0; i < p.k_tiles; ++i) {
-                    if (!mbar_wait_cluster(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
-                                           kStatusProducerWait)) {
+                    if (!mbar_wait<true>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
+                                                 kStatusProducerWait)) {
                         ok = false;
                         break;
                     }
+                    trace(1);   // stage free
                     const uint32_t stage = smem_base + s * PairStage::kBytes;
                     const uint32_t bar = smem_u32(&ctl->full[s]);
                     if (flags & kFlagSkipLoads) {   // timing probe
@@ -217,32 +223,35 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             const uint32_t desc_lo_base = smem_desc_lo(smem_base + PairStage::kOffA);
             const uint32_t sf_ready_bar = smem_u32(&ctl->sf_ready[0]);
             const uint32_t empty_mine = smem_u32(&ctl->empty[0]);
-            const uint32_t empty_peer = map_to_cta(empty_mine, 1);
             const uint32_t sf_base = tmem_base + TM::kSfBase;
-            uint32_t s = 0, a_lo = desc_lo_base, kt = 0, buf = 0;
+            uint32_t s = 0, ph = 0, a_lo = desc_lo_base, buf = 0;
             int it = 0;
             bool failed = false;
+            Tracer trace(p.trace, 0);
             for (int tile = pair; tile < total && !failed; tile += pairs, ++it) {
+                trace(8);
                 if (it > 0) {
                     const int r = it - 1;
-                    if (!mbar_wait_cluster(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
+                    if (!mbar_wait(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
                                            kStatusMmaWaitAcc)) {
                         failed = true;
                         break;
                     }
                     tc_fence_after_sync();
                 }
+                trace(9);   // accumulator buffer available
                 const uint32_t acc_addr = tmem_base + (it & 1) * TM::kAccStride;
 #pragma unroll 1
                 for (int i = 0; i < p.k_tiles; ++i) {
                     // eight arrivals: both CTAs' scale factors are in TMEM; the arriving warps
                     // waited for their CTA's operands first
-                    if (!mbar_wait_cluster(sf_ready_bar + (kt & 3u) * 8u, (kt >> 2) & 1u, abort_flag, p.status,
+                    if (!mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status,
                                            kStatusMmaWaitFull)) {
                         failed = true;
                         break;
                     }
                     tc_fence_after_sync();
+                    trace(1);   // k-tile ready
                     uint32_t b = buf;
 #pragma unroll
                     for (int kb = 0; kb < kKBlocks; ++kb) {
@@ -252,18 +261,16 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
                                                 idesc_mxf4nvf4(256, T::kMmaN), sfa, sfa + 4,
                                                 (kb > 0 || i > 0) ? 1u : 0u);
                     }
-                    tc_commit_pair(empty_mine + s * 8);
-                    tc_commit_pair(empty_peer + s * 8);
-                    ++kt;
+                    tc_commit_pair_both(empty_mine + s * 8, 3);   // both CTAs' `empty` barriers
+                    trace(2);   // k-tile issued
                     buf += kKBlocks / TM::kGranule;
                     if (buf >= static_cast<uint32_t>(TM::kBuffers)) buf -= TM::kBuffers;
                     ++s;
                     a_lo += PairStage::kBytes >> 4;
-                    if (s == kPairStages) { s = 0; a_lo = desc_lo_base; }
+                    if (s == kPairStages) { s = 0; ph ^= 1u; a_lo = desc_lo_base; }
                 }
                 if (failed) break;
-                tc_commit_pair(smem_u32(&ctl->acc_full[it & 1]));
-                tc_commit_pair(map_to_cta(smem_u32(&ctl->acc_full[it & 1]), 1));
+                tc_commit_pair_both(smem_u32(&ctl->acc_full[it & 1]), 3);
             }
             tc_commit_pair(smem_u32(&ctl->aux[0]));
             mbar_wait(smem_u32(&ctl->aux[0]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
@@ -272,20 +279,21 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
     } else if (warp < 4) {
         // ------------------------------ epilogue (each CTA its own 128 rows)
         int it = 0;
+        Tracer trace(warp == 0 && lane == 0 && blockIdx.x == 0 ? p.trace : nullptr, 7);
         for (int tile = pair; tile < total; tile += pairs, ++it) {
             const Work w = pair_work(p, tile, rank);
             const uint32_t release_bar = map_to_cta(smem_u32(&ctl->acc_release[it & 1]), 0);
-            uint32_t good = 1;
-            if (lane == 0)
-                good = mbar_wait_cluster(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
-                                         kStatusEpilogueWait);
-            if (__shfl_sync(0xffffffffu, good, 0) == 0) break;
+            if (!mbar_wait<true>(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
+                                 kStatusEpilogueWait))
+                break;
             tc_fence_after_sync();
+            trace(1);   // accumulator complete
             const bool store = !(flags & kFlagSkipStores);   // timing probe
             if (it & 1)
                 epilogue_tile<Mode::Dual, 1, true>(w, tmem_base, warp, lane, release_bar, store);
             else
                 epilogue_tile<Mode::Dual, 0, true>(w, tmem_base, warp, lane, release_bar, store);
+            trace(2);   // tile stored
             tc_fence_before_sync();
         }
     }

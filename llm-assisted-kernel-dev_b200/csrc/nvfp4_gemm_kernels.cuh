@@ -57,8 +57,9 @@ constexpr int kFlagNoEpilogue = 128;   // epilogue warps idle, the MMA warp does
 struct Tracer {
     unsigned long long* base;
     int n;
-    __device__ Tracer(unsigned long long* trace, int role) : base(trace ? trace + role * 1024 : nullptr), n(0) {
-        if (blockIdx.x != 0) base = nullptr;
+    __device__ Tracer(unsigned long long* trace, int role, unsigned cta = 0)
+        : base(trace ? trace + role * 1024 : nullptr), n(0) {
+        if (blockIdx.x != cta) base = nullptr;
     }
     __device__ __forceinline__ void operator()(unsigned code) {
         if (base && n < 1024) base[n++] = (static_cast<unsigned long long>(code) << 56) |
@@ -284,7 +285,7 @@ struct ControlBlock {
     uint64_t empty[8];
     uint64_t acc_full[2];
     uint64_t acc_release[2];
-    uint64_t sf_ready[4];     // scale factors of k-tile (i mod 4) are in TMEM
+    uint64_t sf_ready[8];     // scale factors of a k-tile are in TMEM (slot: k-tile mod 4, or its stage)
     uint64_t aux[2];
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
@@ -379,8 +380,8 @@ __device__ __forceinline__ void store_chunk(__half* row_ptr, int chunk, const ui
 // accumulator buffers overlap, the 96 shared columns are pulled into registers
 // first and `release` is signalled before any math; their partner columns (the
 // other product of the dual GEMM) are not shared and are read later.
-//   buffer 0 (columns 0-255):   shared = its columns 160-255
-//   buffer 1 (columns 160-415): shared = its columns 0-95
+//   buffer 0 (columns 0-255):   shared = its columns 128-255
+//   buffer 1 (columns 128-383): shared = its columns 0-127
 template <Mode M, int kBuf, bool kReleaseInCluster = false>
 __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base, int quad, int lane,
                                               uint32_t release_bar, bool store = true) {
@@ -402,7 +403,7 @@ __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base,
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-            if constexpr (kReleaseInCluster) mbar_arrive_cluster(release_bar);   // barrier of the pair's first CTA
+            if constexpr (kReleaseInCluster) mbar_arrive_cluster_relaxed(release_bar);   // barrier of the pair's first CTA
             else mbar_arrive(release_bar);
         }
     }
@@ -635,7 +636,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
         uint32_t v[kKBlocks * kWordsPerBlock];
         bool loaded = false;
         auto load_k_tile = [&](uint32_t stage_index, uint32_t phase) -> bool {
-            if (!mbar_wait_warp(smem_u32(&ctl->full[stage_index]), phase, lane, abort_flag, p.status, kStatusSfWait))
+            if (!mbar_wait<true>(smem_u32(&ctl->full[stage_index]), phase, abort_flag, p.status, kStatusSfWait))
                 return false;
             const uint32_t src = smem_base + stage_index * L::kBytes + lane * 16;
 #pragma unroll
@@ -679,8 +680,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                                 if (++rs == kStages) { rs = 0; rph ^= 1u; }
                             }
                             while (ok && retired <= need) {
-                                ok = mbar_wait_warp(smem_u32(&ctl->empty[rs]), rph, lane, abort_flag, p.status,
-                                                    kStatusSfWait);
+                                ok = mbar_wait<true>(smem_u32(&ctl->empty[rs]), rph, abort_flag, p.status, kStatusSfWait);
                                 ++retired;
                                 if (++rs == kStages) { rs = 0; rph ^= 1u; }
                             }
@@ -856,8 +856,8 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                 __syncwarp();
                 if (lane == 0) mbar_arrive(release_bar);
             }
-            if (!mbar_wait_warp(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, lane, abort_flag, p.status,
-                                kStatusEpilogueWait)) {
+            if (!mbar_wait<true>(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
+                                 kStatusEpilogueWait)) {
                 ok = false;
                 break;
             }

@@ -147,6 +147,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Same without release ordering: for hand-overs whose data went to tensor memory
+// (ordered by tcgen05.wait / tcgen05.fence), where nothing in ordinary memory is
+// published by the arrival.  A cluster-scope release otherwise waits for every
+// earlier write of the thread to become visible to the partner SM.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ void cluster_arrive() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 }
@@ -167,6 +174,20 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait_cluster_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+template <bool kParked = false>
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                                   uint32_t* status, uint32_t code) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
@@ -175,7 +196,8 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
     while (true) {
 #pragma unroll 1
         for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait_cluster(bar, parity)) return true;
+            if (kParked ? mbar_try_wait_cluster_parked(bar, parity, 20000u) : mbar_try_wait_cluster(bar, parity))
+                return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > kWaitTimeoutCycles) {
             *abort_flag = 1u;
@@ -371,6 +393,15 @@ __device__ __forceinline__ void tc_mma_mxf4nvf4_pair_lo(uint32_t tmem_d, uint32_
 __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar)
                  : "memory");
+}
+
+// One commit that arrives on the barrier at the same shared-memory offset in every
+// CTA of `cta_mask` (bit i = cluster rank i).
+__device__ __forceinline__ void tc_commit_pair_both(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(cta_mask)
+        : "memory");
 }
 
 // mbarrier arrive once every tcgen05 op issued so far by this thread is done.
