@@ -117,6 +117,9 @@ def cpu_reference_sample(steps: int, warmup: int):
     pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
     from oracle import nvfp4_oracle as orc
     m, n, k = CPU_SAMPLE
+    # the launcher of multi-rank runs exports OMP_NUM_THREADS=1; this arm runs on one
+    # rank only and may use every host core
+    torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))
     data = pkg.inputs.generate_input(m, n, k, 1, 0, dist="uniform16", device="cpu")
     for _ in range(warmup):
         orc.dual_gemm(data)

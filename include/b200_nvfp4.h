@@ -31,7 +31,9 @@ extern "C" {
 #define B200_E_LIMIT (-7)     /* size beyond a documented maximum                */
 
 /* Kernel variants (the `variant` argument of the *_ex entry points). */
-#define B200_VARIANT_AUTO 0       /* library picks by shape                            */
+#define B200_VARIANT_AUTO 0       /* library picks by shape: PAIR for dual GEMMs with
+                                     m % 256 == 0 and at least two 128x128 tiles per SM,
+                                     else PERSISTENT                                    */
 #define B200_VARIANT_PERSISTENT 1 /* warp-specialised persistent kernel               */
 #define B200_VARIANT_SERIAL 2     /* one CTA per tile, single stage (bring-up / debug) */
 #define B200_VARIANT_SERIAL_2MMA 3/* as SERIAL but two N=128 MMAs per k-block          */

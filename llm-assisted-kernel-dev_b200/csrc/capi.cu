@@ -84,6 +84,22 @@ int encode_operand_map(CUtensorMap* map, const void* base, int rows, int k, int 
     return 0;
 }
 
+// fp16 output [batches][rows][ldc] -> 3-D map for TMA stores, box 64 columns x 32 rows
+// (128 bytes wide, the 128-byte-swizzle limit).
+int encode_output_map(CUtensorMap* map, void* base, int rows, int cols, int batches, long long ldc,
+                      long long batch_stride) {
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                          static_cast<cuuint64_t>(batches)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ldc) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
+    cuuint32_t box[3] = {64, 32, 1};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(B200_E_DRIVER, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+    return 0;
+}
+
 // --------------------------------------------------------------------------
 // Per-device state
 // --------------------------------------------------------------------------
@@ -156,17 +172,17 @@ struct DeviceGuard {
 // Dual GEMM
 // --------------------------------------------------------------------------
 struct DualKey {
-    const void *a, *b1, *b2;
+    const void *a, *b1, *b2, *c;
     int m, n, k, l, device;
-    long long b_batch;
+    long long b_batch, ldc, c_batch;
     bool operator==(const DualKey& o) const {
-        return a == o.a && b1 == o.b1 && b2 == o.b2 && m == o.m && n == o.n && k == o.k && l == o.l &&
-               device == o.device && b_batch == o.b_batch;
+        return a == o.a && b1 == o.b1 && b2 == o.b2 && c == o.c && m == o.m && n == o.n && k == o.k && l == o.l &&
+               device == o.device && b_batch == o.b_batch && ldc == o.ldc && c_batch == o.c_batch;
     }
 };
 struct DualMaps {
     DualKey key;
-    CUtensorMap a, b1, b2;
+    CUtensorMap a, b1, b2, c;
 };
 std::vector<DualMaps> g_dual_cache;   // small most-recently-used list
 
@@ -288,7 +304,7 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
 
     DenseProblem p;
     memset(&p, 0, sizeof p);
-    DualKey key{a, b1, b2, m, n, k, l, device, b_batch_bytes};
+    DualKey key{a, b1, b2, c, m, n, k, l, device, b_batch_bytes, ldc, c_batch};
     const DualMaps* maps = nullptr;
     for (const DualMaps& e : g_dual_cache)
         if (e.key == key) { maps = &e; break; }
@@ -299,6 +315,7 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
         if ((rc = encode_operand_map(&fresh.a, a, m, k, l, static_cast<long long>(m) * (k / 2)))) return rc;
         if ((rc = encode_operand_map(&fresh.b1, b1, n, k, l, b_batch_bytes))) return rc;
         if ((rc = encode_operand_map(&fresh.b2, b2, n, k, l, b_batch_bytes))) return rc;
+        if ((rc = encode_output_map(&fresh.c, c, m, n, l, ldc, c_batch))) return rc;
         if (g_dual_cache.size() >= 16) g_dual_cache.erase(g_dual_cache.begin());
         g_dual_cache.push_back(fresh);
         maps = &g_dual_cache.back();
@@ -306,6 +323,7 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     p.map_a = maps->a;
     p.map_b1 = maps->b1;
     p.map_b2 = maps->b2;
+    p.map_c = maps->c;
     p.sfa = static_cast<const uint8_t*>(sfa);
     p.sfb1 = static_cast<const uint8_t*>(sfb1);
     p.sfb2 = static_cast<const uint8_t*>(sfb2);
@@ -354,6 +372,10 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
         if (p.m_tiles % 2) return fail(B200_E_SHAPE, "dual gemm: CTA pairs need m to be a multiple of 256 (m=%d)", m);
         return launch_pair(p, st->sm_count, 0, s);
     }
+    // AUTO: CTA pairs when the row tiles pair up and every SM gets at least two tiles
+    // (with fewer the one-CTA kernel's finer tiles balance better).
+    if (variant == B200_VARIANT_AUTO && p.m_tiles % 2 == 0 && p.total_tiles >= 2 * st->sm_count)
+        return launch_pair(p, st->sm_count, 0, s);
     switch (variant) {
         case B200_VARIANT_SERIAL:
             return launch_serial<Mode::Dual>(p, p.total_tiles, 0, s);

@@ -36,7 +36,10 @@ struct PairStage {
     static constexpr uint32_t kBytes = kOffSfB2 + kSfChunkBytes;        // 38 KiB, multiple of 1024
 };
 constexpr int kPairStages = 5;
-constexpr uint32_t kPairSmemBytes = 1024u + kPairStages * PairStage::kBytes + sizeof(ControlBlock);
+constexpr uint32_t kPairStagingBytes = 4u * 8192u;   // per epilogue warp: two boxes of 32 rows x 128 bytes
+constexpr uint32_t kPairSmemBytes =
+    1024u + kPairStages * PairStage::kBytes + kPairStagingBytes + sizeof(ControlBlock);
+static_assert(kPairSmemBytes <= 227u * 1024u, "shared memory budget");
 constexpr uint32_t kStatusPairWait = 0x80;
 
 // Work of one CTA of the pair for pair-tile `tile`: rows of A/C are those of the
@@ -78,7 +81,8 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     ControlBlock* ctl = reinterpret_cast<ControlBlock*>(smem_raw + (smem_base - smem_u32(smem_raw)) +
-                                                        kPairStages * PairStage::kBytes);
+                                                        kPairStages * PairStage::kBytes + kPairStagingBytes);
+    const uint32_t staging_base = smem_base + kPairStages * PairStage::kBytes;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_cta_rank();          // 0: issues the MMAs, 1: partner
@@ -289,13 +293,17 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             tc_fence_after_sync();
             trace(1);   // accumulator complete
             const bool store = !(flags & kFlagSkipStores);   // timing probe
+            const uint32_t staging = staging_base + static_cast<uint32_t>(warp) * 8192u;
+            const int c_col = w.blo_row, c_row = w.a_row + warp * 32;
             if (it & 1)
-                epilogue_tile<Mode::Dual, 1, true>(w, tmem_base, warp, lane, release_bar, store);
+                epilogue_tile_staged<1>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store);
             else
-                epilogue_tile<Mode::Dual, 0, true>(w, tmem_base, warp, lane, release_bar, store);
+                epilogue_tile_staged<0>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store);
             trace(2);   // tile stored
             tc_fence_before_sync();
         }
+        if (lane == 0) bulk_wait_group_all();   // the last boxes are in global memory before the CTA exits
+        __syncwarp();
     }
     // Nobody leaves while the partner may still signal its barriers or while MMAs
     // issued by the first CTA still run on this SM.

@@ -15,6 +15,9 @@
 // N=256 MMA per 64-k block produces both products (A and its scale factors are
 // staged once): accumulator columns [0,128) = A.B1^T, [128,256) = A.B2^T.
 #pragma once
+#ifndef B200_EXP_STG
+#define B200_EXP_STG 0
+#endif
 
 #include "ptx_sm100.cuh"
 
@@ -92,6 +95,7 @@ template <> struct ModeTraits<Mode::Group256> {
 // Dual GEMM: lives in kernel parameter space (tensor maps need 64-byte alignment).
 struct alignas(64) DenseProblem {
     CUtensorMap map_a, map_b1, map_b2;   // 3-D {k/2 bytes, rows, batch}, box {128, 128, 1}
+    CUtensorMap map_c;                   // 3-D {n, m, batch} fp16, box {64, 32, 1}, 128-byte swizzle (pair kernel)
     const uint8_t* sfa;
     const uint8_t* sfb1;
     const uint8_t* sfb2;
@@ -265,15 +269,15 @@ template <Mode M> struct StageLayout {
 template <Mode M> struct TmemMap {
     using T = ModeTraits<M>;
     static constexpr bool kOverlapped = (T::kMmaN == 256);
-    static constexpr uint32_t kAccStride = 128;
-    static constexpr uint32_t kSharedBegin = 128;                      // columns shared by the two buffers
-    static constexpr uint32_t kSfBase = kOverlapped ? 384 : 256;
+    static constexpr uint32_t kAccStride = kOverlapped ? 112 : 128;
+    static constexpr uint32_t kSharedBegin = kAccStride;               // buffer 0's first column that buffer 1 also uses
+    static constexpr uint32_t kSfBase = kOverlapped ? 368 : 256;
     static constexpr uint32_t kSfBCols = T::kMmaN / 32;
     static constexpr uint32_t kSlotCols = 4 + kSfBCols;
     static constexpr int kGranule = kOverlapped ? 2 : 4;              // 64-k blocks per hand-over
-    static constexpr int kBuffers = kOverlapped ? 5 : 4;              // hand-over units in the ring
+    static constexpr int kBuffers = kOverlapped ? 6 : 4;              // hand-over units in the ring
     static constexpr int kSlots = kGranule * kBuffers;
-    static constexpr int kEarlyChunks = kOverlapped ? 8 : 0;          // 128 shared columns / 16
+    static constexpr int kEarlyChunks = kOverlapped ? 9 : 0;          // 144 shared columns / 16
     static_assert(kSfBase + kSlots * kSlotCols <= kTmemColumns, "TMEM budget");
     static_assert(kKBlocks % kGranule == 0 && kBuffers <= 8, "ring shape");
     __device__ static constexpr uint32_t sfa_col(int slot) { return kSfBase + slot * kSlotCols; }
@@ -372,8 +376,13 @@ __device__ __forceinline__ void store_chunk(__half* row_ptr, int chunk, const ui
         packed[i] = pack_half2(a, b);
     }
     __half* dst = row_ptr + chunk * 16;
+#if B200_EXP_STG == 1
+    if (packed[0] == 0x7fc17fc2u && packed[5] == 0x12345678u)
+#endif
+    {
     st_global_v4(dst, packed[0], packed[1], packed[2], packed[3]);
     st_global_v4(dst + 8, packed[4], packed[5], packed[6], packed[7]);
+    }
 }
 
 // Epilogue of one tile for one warp (TMEM lane quadrant `quad`).  When the
@@ -429,6 +438,78 @@ __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base,
             for (int i = 0; i < 16; ++i) y[i] = early[(ycol - kSharedRel) / 16][i];
         }
         if (row_ok && chunk * 16 < w.cols_valid) store_chunk<T::kSilu>(row_ptr, chunk, x, T::kSilu ? y : x);
+    }
+}
+
+// Dual-GEMM epilogue that leaves through shared memory and TMA stores (CTA-pair
+// kernel).  With one output row per TMEM lane a thread's direct global stores are
+// 16 bytes at a 2*ldc-byte pitch: every warp-wide store touches 32 different lines
+// and occupies the SM's load/store path (which it shares with shared memory) for 32
+// cycles instead of 4.  Here each warp converts its 32 rows x 128 columns into an
+// 8 KB staging area (two boxes of 32 rows x 128 bytes in the 128-byte-swizzle layout,
+// conflict-free for the 16-byte stores) and one lane hands each box to the TMA unit
+// as soon as its 64 columns are done.  `staging` is the warp's own area (1024-byte
+// aligned); a box is only rewritten after the previous tile's store has read it.
+template <int kBuf>
+__device__ __forceinline__ void epilogue_tile_staged(const DenseProblem& p, const Work& w, uint32_t tmem_base,
+                                                     int quad, int lane, uint32_t release_bar, uint32_t staging,
+                                                     int c_col, int c_row, bool store) {
+    using TM = TmemMap<Mode::Dual>;
+    constexpr int kEarly = TM::kEarlyChunks;
+    constexpr int kSharedRel = (kBuf == 0) ? TM::kSharedBegin : 0;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
+    uint32_t early[kEarly][16];
+    static_assert(kEarly == 9, "the shared columns are fetched as 64 + 64 + 16");
+    tc_ld_x64(acc + kSharedRel, &early[0][0]);
+    tc_ld_x64(acc + kSharedRel + 64, &early[4][0]);
+    tc_ld_x16(acc + kSharedRel + 128, early[8]);
+    tc_wait_ld();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) {
+        mbar_arrive_cluster_relaxed(release_bar);   // barrier of the pair's first CTA
+        bulk_wait_group_read_all();                  // the previous tile's boxes have left the staging area
+    }
+    __syncwarp();
+    const uint32_t row_base = staging + lane * 128;
+    const uint32_t swz = static_cast<uint32_t>(lane & 7);
+#pragma unroll
+    for (int chunk = 0; chunk < 8; ++chunk) {
+        const int xcol = chunk * 16;
+        const int ycol = 128 + chunk * 16;
+        const bool x_early = xcol >= kSharedRel && xcol < kSharedRel + kEarly * 16;
+        const bool y_early = ycol >= kSharedRel && ycol < kSharedRel + kEarly * 16;
+        uint32_t x[16], y[16];
+        if (!x_early) tc_ld_x16(acc + xcol, x);
+        if (!y_early) tc_ld_x16(acc + ycol, y);
+        if (!x_early || !y_early) tc_wait_ld();
+        if (x_early) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = early[(xcol - kSharedRel) / 16][i];
+        }
+        if (y_early) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y[i] = early[(ycol - kSharedRel) / 16][i];
+        }
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            packed[i] = pack_half2(silu_mul(__uint_as_float(x[2 * i]), __uint_as_float(y[2 * i])),
+                                   silu_mul(__uint_as_float(x[2 * i + 1]), __uint_as_float(y[2 * i + 1])));
+        // box = chunk / 4 (64 columns each); inside it this chunk is 16-byte units 2*(chunk%4), +1
+        const uint32_t box = row_base + static_cast<uint32_t>(chunk >> 2) * 4096u;
+        const uint32_t u0 = static_cast<uint32_t>((chunk & 3) * 2);
+        st_shared_v4(box + ((u0 ^ swz) << 4), packed[0], packed[1], packed[2], packed[3]);
+        st_shared_v4(box + (((u0 + 1) ^ swz) << 4), packed[4], packed[5], packed[6], packed[7]);
+        if ((chunk & 3) == 3) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && store) {
+                tma_store_3d(&p.map_c, staging + static_cast<uint32_t>(chunk >> 2) * 4096u, c_col + (chunk >> 2) * 64,
+                             c_row, w.batch);
+                bulk_commit_group();
+            }
+        }
     }
 }
 

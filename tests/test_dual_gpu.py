@@ -56,7 +56,11 @@ def test_batched_l3(pkg, oracle, variant):
 def test_many_tiles_per_cta(pkg, oracle):
     # 64 x 24 = 1536 tiles > 148 SMs: every CTA walks several tiles, both TMEM buffers
     data = pkg.inputs.generate_input(8192, 3072, 256, 1, 3, dist="reference", device="cuda")
-    _check(oracle, data, _run(pkg, data, V_PERSISTENT), TOL_REFERENCE)
+    one_cta = _run(pkg, data, V_PERSISTENT).clone()
+    _check(oracle, data, one_cta, TOL_REFERENCE)
+    # with this many tiles the library's own choice is the CTA-pair kernel: same bits
+    auto = _run(pkg, data, V_AUTO)
+    assert torch.equal(auto.view(torch.int16), one_cta.view(torch.int16))
 
 
 def test_benchmark_shape_skinny(pkg, oracle):
