@@ -14,10 +14,11 @@ value      algorithmic TFLOP/s (4*M*N*K per step), inputs resident in HBM
 e2e        same metric through custom_kernel() with host buffers: pinned-host ->
            device copies of every input and a device -> host read of C inside
            the timed region
-roofline   tensor-core roofline of the dual-GEMM kernel
+roofline   tensor-core roofline of the dual-GEMM kernel: algorithmic FLOP per launch /
+           CUDA-event time, against 4 x the measured cuBLAS bf16 rate
 cpu_baseline / --impl reference
            the reference's fp32 dequantise-then-matmul CPU path (torch CPU ops,
-           all host threads) on a bounded sample of the same workload
+           all host threads) on the same workload, a few passes
 extra      the other benchmark configurations (skinny-M dual GEMM, G=8 grouped
            GEMM, 64-expert MoE grouped GEMM) in microseconds per launch
 """
@@ -42,8 +43,8 @@ METRIC = "nvfp4_dual_gemm_tflops"
 UNIT = "TFLOP/s"
 L2_BYTES = 126 * 1024 * 1024
 NOMINAL_FP4_TFLOPS = 9000.0
-# CPU sample: a (rows x cols) corner of the same problem, full K
-CPU_SAMPLE = (2048, 3584, K)
+# CPU sample of the same problem
+CPU_SAMPLE = (M, N, K)          # the whole workload: about 1.5-5 s per pass on 8-16 host cores
 
 
 def load_peaks():
@@ -112,7 +113,7 @@ class ClockSampler:
 # --------------------------------------------------------------------------- reference arm (CPU)
 def cpu_reference_sample(steps: int, warmup: int):
     """The reference's CPU check (fp32 dequantise, matmul, silu*mul, fp16 cast)
-    on a corner of the benchmark problem.  Returns (TFLOP/s, seconds per step, threads)."""
+    on the benchmark problem.  Returns (TFLOP/s, seconds per step, threads)."""
     import torch
     pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
     from oracle import nvfp4_oracle as orc
@@ -135,13 +136,13 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 20))
-    tflops, dt, threads = cpu_reference_sample(steps, max(1, min(args.warmup, 3)))
+    steps = max(1, min(args.steps, 10))
+    tflops, dt, threads = cpu_reference_sample(steps, max(1, min(args.warmup, 2)))
     m, n, k = CPU_SAMPLE
-    sample = f"rows 0-{m - 1} x cols 0-{n - 1} of the workload, full K={k} (4*{m}*{n}*{k} flop per step)"
+    sample = f"the whole workload per step: {m}x{n}x{k} (4*{m}*{n}*{k} flop), {steps} timed passes"
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": max(1, min(args.warmup, 3)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 (dequantised e2m1 x e4m3)", "data": "synthetic",
         "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "l": 1,
                    "path": "reference CPU check: fp32 dequantise-then-matmul, silu*mul, fp16 cast (torch CPU ops)"},
@@ -334,7 +335,7 @@ def run_ours(args):
         "bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
         "peak_basis": f"4 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no measured FP4 "
                       f"figure exists; nominal dense NVFP4 is {NOMINAL_FP4_TFLOPS:.0f}",
-        "frac_nominal": achieved / NOMINAL_FP4_TFLOPS, "kernel": "nvfp4_gemm_persistent<Dual>",
+        "frac_nominal": achieved / NOMINAL_FP4_TFLOPS, "kernel": "nvfp4_dual_gemm_pair",
         "avg_launch_us": sec / args.steps * 1e6, "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
         "algorithmic_bytes": pkg.formats.dual_gemm_bytes(M, n_local, K),
     }
@@ -353,10 +354,10 @@ def run_ours(args):
         "clocks": clocks, "roofline": roofline,
     }
     if world == 1:
-        cpu_tflops, cpu_dt, threads = cpu_reference_sample(3, 1)
+        cpu_tflops, cpu_dt, threads = cpu_reference_sample(4, 1)
         m_, n_, k_ = CPU_SAMPLE
         line["cpu_baseline"] = {"value": cpu_tflops, "unit": UNIT, "cores": threads, "kind": "port",
-                                "sample": f"{m_}x{n_} corner of the workload, full K={k_}, 3 timed passes "
+                                "sample": f"the whole workload ({m_}x{n_}x{k_}), 4 timed passes "
                                           f"({cpu_dt:.2f} s each)"}
         if not args.no_extra:
             del dev_sets, host_sets
@@ -367,9 +368,11 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of one full-size dual-GEMM launch, from the ncu capture
-# summarised in profiles/; None until measured.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) of one full-size dual-GEMM launch: dram__bytes_read.sum 85.6 MB +
+# dram__bytes_write.sum 194.6 MB from a one-pass ncu capture of `bench.py --kernel-only`
+# (summary under profiles/).  Reads are the operands once;
+# part of C is still in the L2 when the launch ends.
+TRAFFIC_BYTES_PER_LAUNCH = 280.2e6
 
 
 def main():

@@ -42,7 +42,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
            "-gencode", "arch=compute_100a,code=sm_100a",
            "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",
            "-Xptxas", "-v" if verbose else "-O3",
-           "-o", LIB] + os.environ.get("B200_NVCC_EXTRA", "").split() + [os.path.join(CSRC, s) for s in SOURCES]
+           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)

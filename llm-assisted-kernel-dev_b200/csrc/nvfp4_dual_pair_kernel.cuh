@@ -136,6 +136,7 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
                 trace(1);   // operands landed
                 uint32_t v[kKBlocks * 12];
                 const uint32_t src = smem_base + s * PairStage::kBytes + lane * 16;
+                if (!(flags & kFlagSkipBHi))   // timing probe (bit reused): no scale-factor reads at all
 #pragma unroll
                 for (int kb = 0; kb < kKBlocks; ++kb) {
                     uint32_t* d = v + kb * 12;
@@ -232,6 +233,7 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             int it = 0;
             bool failed = false;
             Tracer trace(p.trace, 0);
+            const long long kernel_t0 = clock64();
             for (int tile = pair; tile < total && !failed; tile += pairs, ++it) {
                 trace(8);
                 if (it > 0) {
@@ -278,6 +280,7 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             }
             tc_commit_pair(smem_u32(&ctl->aux[0]));
             mbar_wait(smem_u32(&ctl->aux[0]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
+            if (p.trace && blockIdx.x == 0) p.trace[8 * 1024 - 1] = static_cast<unsigned long long>(clock64() - kernel_t0);
         }
         __syncwarp();
     } else if (warp < 4) {

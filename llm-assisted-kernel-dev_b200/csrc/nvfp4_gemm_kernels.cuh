@@ -15,9 +15,6 @@
 // N=256 MMA per 64-k block produces both products (A and its scale factors are
 // staged once): accumulator columns [0,128) = A.B1^T, [128,256) = A.B2^T.
 #pragma once
-#ifndef B200_EXP_STG
-#define B200_EXP_STG 0
-#endif
 
 #include "ptx_sm100.cuh"
 
@@ -376,13 +373,8 @@ __device__ __forceinline__ void store_chunk(__half* row_ptr, int chunk, const ui
         packed[i] = pack_half2(a, b);
     }
     __half* dst = row_ptr + chunk * 16;
-#if B200_EXP_STG == 1
-    if (packed[0] == 0x7fc17fc2u && packed[5] == 0x12345678u)
-#endif
-    {
     st_global_v4(dst, packed[0], packed[1], packed[2], packed[3]);
     st_global_v4(dst + 8, packed[4], packed[5], packed[6], packed[7]);
-    }
 }
 
 // Epilogue of one tile for one warp (TMEM lane quadrant `quad`).  When the
