@@ -125,8 +125,7 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
         constexpr uint32_t kUnitsPerKTile = kKBlocks / TM::kGranule;
         uint32_t s = 0, ph = 0, kt = 0, buf = 0, units = 0, retired = 0, rs = 0, rph = 0;
         bool ok = true;
-        Tracer trace(lane == 0 && blockIdx.x < 2 && (rank == 0 || warp == 6 || warp == 9) ? p.trace : nullptr,
-                     rank == 0 ? warp - 5 : (warp == 6 ? 5 : 6), rank);
+        Tracer trace(nullptr, 0);
         for (int tile = pair; ok && tile < total; tile += pairs) {
             for (int i = 0; ok && i < p.k_tiles; ++i) {
                 if (!mbar_wait<true>(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusSfWait)) {
@@ -236,6 +235,12 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             const long long kernel_t0 = clock64();
             for (int tile = pair; tile < total && !failed; tile += pairs, ++it) {
                 trace(8);
+                // the first k-tile's scale factors are normally in place long before the
+                // accumulator comes back: pass that barrier first, off the hand-back path
+                if (!mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull)) {
+                    failed = true;
+                    break;
+                }
                 if (it > 0) {
                     const int r = it - 1;
                     if (!mbar_wait(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
@@ -243,20 +248,21 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
                         failed = true;
                         break;
                     }
-                    tc_fence_after_sync();
                 }
+                tc_fence_after_sync();   // orders the MMAs below after both barriers
                 trace(9);   // accumulator buffer available
                 const uint32_t acc_addr = tmem_base + (it & 1) * TM::kAccStride;
 #pragma unroll 1
                 for (int i = 0; i < p.k_tiles; ++i) {
                     // eight arrivals: both CTAs' scale factors are in TMEM; the arriving warps
                     // waited for their CTA's operands first
-                    if (!mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status,
-                                           kStatusMmaWaitFull)) {
-                        failed = true;
-                        break;
+                    if (i > 0) {
+                        if (!mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull)) {
+                            failed = true;
+                            break;
+                        }
+                        tc_fence_after_sync();
                     }
-                    tc_fence_after_sync();
                     trace(1);   // k-tile ready
                     uint32_t b = buf;
 #pragma unroll
@@ -286,7 +292,7 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
     } else if (warp < 4) {
         // ------------------------------ epilogue (each CTA its own 128 rows)
         int it = 0;
-        Tracer trace(warp == 0 && lane == 0 && blockIdx.x == 0 ? p.trace : nullptr, 7);
+        Tracer trace(lane == 0 && blockIdx.x == 0 ? p.trace : nullptr, warp == 0 ? 7 : warp);
         for (int tile = pair; tile < total; tile += pairs, ++it) {
             const Work w = pair_work(p, tile, rank);
             const uint32_t release_bar = map_to_cta(smem_u32(&ctl->acc_release[it & 1]), 0);
@@ -299,9 +305,9 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             const uint32_t staging = staging_base + static_cast<uint32_t>(warp) * 8192u;
             const int c_col = w.blo_row, c_row = w.a_row + warp * 32;
             if (it & 1)
-                epilogue_tile_staged<1>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store);
+                epilogue_tile_staged<1>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store, &trace);
             else
-                epilogue_tile_staged<0>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store);
+                epilogue_tile_staged<0>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store, &trace);
             trace(2);   // tile stored
             tc_fence_before_sync();
         }

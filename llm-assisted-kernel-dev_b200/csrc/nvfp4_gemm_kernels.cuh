@@ -445,7 +445,7 @@ __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base,
 template <int kBuf>
 __device__ __forceinline__ void epilogue_tile_staged(const DenseProblem& p, const Work& w, uint32_t tmem_base,
                                                      int quad, int lane, uint32_t release_bar, uint32_t staging,
-                                                     int c_col, int c_row, bool store) {
+                                                     int c_col, int c_row, bool store, Tracer* tr = nullptr) {
     using TM = TmemMap<Mode::Dual>;
     constexpr int kEarly = TM::kEarlyChunks;
     constexpr int kSharedRel = (kBuf == 0) ? TM::kSharedBegin : 0;
@@ -455,11 +455,14 @@ __device__ __forceinline__ void epilogue_tile_staged(const DenseProblem& p, cons
     tc_ld_x64(acc + kSharedRel, &early[0][0]);
     tc_ld_x64(acc + kSharedRel + 64, &early[4][0]);
     tc_ld_x16(acc + kSharedRel + 128, early[8]);
+    if (tr) (*tr)(5);
     tc_wait_ld();
+    if (tr) (*tr)(6);
     tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) {
         mbar_arrive_cluster_relaxed(release_bar);   // barrier of the pair's first CTA
+        if (tr) (*tr)(7);
         bulk_wait_group_read_all();                  // the previous tile's boxes have left the staging area
     }
     __syncwarp();
