@@ -39,8 +39,9 @@ extern "C" {
 #define B200_VARIANT_SERIAL_2MMA 3/* as SERIAL but two N=128 MMAs per k-block          */
 #define B200_VARIANT_SPLITK 4     /* persistent kernel, k-range split over CTAs with an
                                      fp32 partial-sum exchange before the epilogue     */
-#define B200_VARIANT_PAIR 5       /* dual GEMM on CTA pairs (2-SM MMA, 256-row tiles);
-                                     needs m % 256 == 0                                 */
+#define B200_VARIANT_PAIR 5       /* CTA pairs (2-SM MMA, 256-row tiles).  Dual GEMM:
+                                     needs m % 256 == 0.  Grouped GEMM: 256 x 256 tiles,
+                                     needs every n % 256 == 0, any m                    */
 
 /* Dual GEMM only: variant = B200_VARIANT_PROBE_BASE + bits runs the persistent
  * kernel with parts of its data path switched off (bit 1: scale-factor stores,

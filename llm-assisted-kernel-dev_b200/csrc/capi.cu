@@ -11,7 +11,7 @@
 
 #include "../../include/b200_nvfp4.h"
 #include "nvfp4_gemm_kernels.cuh"
-#include "nvfp4_dual_pair_kernel.cuh"
+#include "nvfp4_pair_kernels.cuh"
 
 namespace b200 {
 namespace {
@@ -142,7 +142,8 @@ int device_state(int device, DeviceState** out) {
                               smem_bytes_persistent<Mode::Group128, kG128Stages>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Group256, kG256Stages>,
                               smem_bytes_persistent<Mode::Group256, kG256Stages>()))) return rc;
-        if ((rc = opt_in_smem(nvfp4_dual_gemm_pair, kPairSmemBytes))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDual>, kPairSmemBytes))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairGrouped>, kPairSmemBytes))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Dual>, smem_bytes_serial<Mode::Dual>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group128>, smem_bytes_serial<Mode::Group128>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group256>, smem_bytes_serial<Mode::Group256>()))) return rc;
@@ -233,8 +234,8 @@ int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStr
 }
 
 // CTA pairs: clusters of two CTAs, one pair per TPC, each pair walks pair tiles.
-int launch_pair(const DenseProblem& prob, int sm_count, int flags, cudaStream_t stream) {
-    const int pair_tiles = (prob.m_tiles / 2) * prob.n_tiles * prob.batches;
+template <typename S> int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, int flags,
+                                      cudaStream_t stream) {
     int pairs = sm_count / 2;
     if (pairs > pair_tiles) pairs = pair_tiles;
     cudaLaunchConfig_t cfg;
@@ -250,10 +251,11 @@ int launch_pair(const DenseProblem& prob, int sm_count, int flags, cudaStream_t 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B200_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_dual_gemm_pair, prob, flags));
+    B200_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair<S>, prob, flags));
     ++g_launches;
     return 0;
 }
+int dual_pair_tiles(const DenseProblem& p) { return (p.m_tiles / 2) * p.n_tiles * p.batches; }
 
 template <Mode M, typename P> int launch_serial(const P& prob, int units, int two_mma, cudaStream_t stream) {
     nvfp4_gemm_serial<M><<<units, 128, smem_bytes_serial<M>(), stream>>>(prob, two_mma);
@@ -367,15 +369,15 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     if (p.k_splits > 1)
         return launch_persistent<Mode::Dual, kDualStages>(p, p.total_tiles * p.k_splits, st->sm_count, 0, s);
     if (pair_probe && p.m_tiles % 2 == 0)
-        return launch_pair(p, st->sm_count, variant - B200_VARIANT_PROBE_BASE - 300, s);
+        return launch_pair<PairDual>(p, dual_pair_tiles(p), st->sm_count, variant - B200_VARIANT_PROBE_BASE - 300, s);
     if (variant == B200_VARIANT_PAIR) {
         if (p.m_tiles % 2) return fail(B200_E_SHAPE, "dual gemm: CTA pairs need m to be a multiple of 256 (m=%d)", m);
-        return launch_pair(p, st->sm_count, 0, s);
+        return launch_pair<PairDual>(p, dual_pair_tiles(p), st->sm_count, 0, s);
     }
     // AUTO: CTA pairs when the row tiles pair up and every SM gets at least two tiles
     // (with fewer the one-CTA kernel's finer tiles balance better).
     if (variant == B200_VARIANT_AUTO && p.m_tiles % 2 == 0 && p.total_tiles >= 2 * st->sm_count)
-        return launch_pair(p, st->sm_count, 0, s);
+        return launch_pair<PairDual>(p, dual_pair_tiles(p), st->sm_count, 0, s);
     switch (variant) {
         case B200_VARIANT_SERIAL:
             return launch_serial<Mode::Dual>(p, p.total_tiles, 0, s);
@@ -421,12 +423,13 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
                                uint32_t* status) {
     if (groups <= 0) return fail(B200_E_SHAPE, "grouped gemm: groups=%d must be positive", groups);
     if (!a || !b || !sfa || !sfb || !c || !mnk) return fail(B200_E_NULL, "grouped gemm: NULL argument array");
-    if (variant != B200_VARIANT_AUTO && variant != B200_VARIANT_PERSISTENT && variant != B200_VARIANT_SERIAL)
+    if (variant != B200_VARIANT_AUTO && variant != B200_VARIANT_PERSISTENT && variant != B200_VARIANT_SERIAL &&
+        variant != B200_VARIANT_PAIR)
         return fail(B200_E_VARIANT, "grouped gemm: unknown variant %d", variant);
     if (tile_n != 0 && tile_n != 128 && tile_n != 256)
         return fail(B200_E_VARIANT, "grouped gemm: tile_n=%d must be 0, 128 or 256", tile_n);
     bool all_n256 = true;
-    long long tiles128 = 0;
+    long long tiles128 = 0, pair_tiles = 0;
     for (int g = 0; g < groups; ++g) {
         const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
         if (m < 0 || n <= 0 || k <= 0)
@@ -440,7 +443,10 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
             return fail(B200_E_ALIGN, "grouped gemm: group %d has a pointer that is not 16-byte aligned", g);
         if (n % 256) all_n256 = false;
         tiles128 += static_cast<long long>((m + 127) / 128) * (n / 128);
+        pair_tiles += static_cast<long long>((m + 255) / 256) * (n / 256);
     }
+    if (variant == B200_VARIANT_PAIR && !all_n256)
+        return fail(B200_E_SHAPE, "grouped gemm: CTA pairs need every n to be a multiple of 256");
     if (!workspace) return fail(B200_E_WORKSPACE, "grouped gemm: workspace is NULL");
     if (reinterpret_cast<uintptr_t>(workspace) & 255u)
         return fail(B200_E_WORKSPACE, "grouped gemm: workspace must be 256-byte aligned");
@@ -458,7 +464,13 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
 
     // Wide tiles halve the A traffic per flop; keep 128-wide tiles when they are
     // needed to give every SM work or when some n is not a multiple of 256.
+    const bool tile_n_chosen_here = tile_n == 0;
     if (tile_n == 0) tile_n = (all_n256 && tiles128 / 2 >= 2LL * st->sm_count) ? 256 : 128;
+    // CTA pairs (256 x 256 tiles): on request, or by default when every n allows it and
+    // each pair of SMs gets at least two tiles
+    const bool use_pair = variant == B200_VARIANT_PAIR ||
+                          (variant == B200_VARIANT_AUTO && tile_n_chosen_here && all_n256 && pair_tiles >= st->sm_count);
+    if (use_pair) tile_n = -256;   // marks the pair tiling in the cache key and the table
 
     std::vector<uint8_t> key(sizeof(int) * 2 + groups * (5 * sizeof(void*) + 3 * sizeof(int)));
     {
@@ -485,8 +497,8 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
             e.m = m;
             e.n = n;
             e.k_tiles = k / 256;
-            e.m_tiles = (m + 127) / 128;
-            e.n_tiles = (n + tile_n - 1) / tile_n;
+            e.m_tiles = use_pair ? (m + 255) / 256 : (m + 127) / 128;
+            e.n_tiles = use_pair ? n / 256 : (n + tile_n - 1) / tile_n;
             e.tile_begin = tile_begin;
             e.sf_k_atoms = k / 64;
             e.sfb_row_atoms = n / 128;
@@ -518,6 +530,7 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     p.total_tiles = cur.total_tiles;
     p.status = status ? status : st->status;
     p.trace = nullptr;
+    if (cur.tile_n == -256) return launch_pair<PairGrouped>(p, p.total_tiles, st->sm_count, 0, s);
     if (variant == B200_VARIANT_SERIAL) {
         return cur.tile_n == 256 ? launch_serial<Mode::Group256>(p, p.total_tiles, 0, s)
                                  : launch_serial<Mode::Group128>(p, p.total_tiles, 0, s);

@@ -1,5 +1,8 @@
-// Dual GEMM on CTA pairs (tcgen05 cta_group::2): two CTAs on the two SMs of a TPC
-// share one 256 x 128 output tile of C = silu(A.B1^T) * (A.B2^T).
+// GEMMs on CTA pairs (tcgen05 cta_group::2): two CTAs on the two SMs of a TPC share
+// one 256-row output tile.  Dual GEMM: 256 x 128 outputs of C = silu(A.B1^T) * (A.B2^T)
+// (merged B = the B1 tile in the first CTA, the B2 tile in the second).  Grouped GEMM:
+// 256 x 256 outputs of one group's C = A.B^T (merged B = 256 consecutive rows of B, 128
+// in each CTA); rows past the group's M are zero-filled by TMA and never stored.
 //
 // Why: in the one-CTA kernel a 128x256x64 MMA reads 12 KB of operands from shared
 // memory (A 4 KB + merged B 8 KB) every 130 cycles, the TMA fills add 54 KB per
@@ -42,42 +45,161 @@ constexpr uint32_t kPairSmemBytes =
 static_assert(kPairSmemBytes <= 227u * 1024u, "shared memory budget");
 constexpr uint32_t kStatusPairWait = 0x80;
 
-// Work of one CTA of the pair for pair-tile `tile`: rows of A/C are those of the
-// CTA's rank, the B tile is B1 for rank 0 and B2 for rank 1.
-__device__ __forceinline__ Work pair_work(const DenseProblem& p, int tile, uint32_t rank) {
-    const int m_pairs = p.m_tiles / 2;
-    const int m_pair = tile % m_pairs;
-    const int t = tile / m_pairs;
-    const int n_blk = t % p.n_tiles;
-    const int b = t / p.n_tiles;
-    const int m_blk = 2 * m_pair + static_cast<int>(rank);
-    Work w;
-    w.map_a = &p.map_a;
-    w.map_blo = rank == 0 ? static_cast<const void*>(&p.map_b1) : static_cast<const void*>(&p.map_b2);
-    w.map_bhi = w.map_blo;
-    w.a_row = m_blk * kTileM;
-    w.blo_row = w.bhi_row = n_blk * 128;
-    w.batch = b;
-    const long long sf_row = static_cast<long long>(p.sf_k_atoms) * kSfAtomBytes;
-    w.sfa = p.sfa + b * p.sfa_batch + m_blk * sf_row;
-    w.sfblo = p.sfb1 + b * p.sfb_batch + n_blk * sf_row;
-    w.sfbhi = p.sfb2 + b * p.sfb_batch + n_blk * sf_row;
-    w.ldc = p.ldc;
-    w.c = p.c + b * p.c_batch + static_cast<long long>(m_blk) * kTileM * p.ldc + n_blk * 128;
-    w.rows_valid = kTileM;
-    w.cols_valid = 128;
-    w.k_tile_begin = 0;
-    w.k_tile_count = p.k_tiles;
-    w.group = 0;
-    w.tile = tile;
-    w.split = 0;
-    return w;
+// Scheduling policies: work of one CTA (cluster rank) of the pair for pair tile `tile`.
+struct PairDual {
+    using Params = DenseProblem;
+    static constexpr bool kGrouped = false;
+    __device__ static int total(const Params& p) { return (p.m_tiles / 2) * p.n_tiles * p.batches; }
+    __device__ static int k_tiles(const Params& p, int /*tile*/, int& /*cursor*/) { return p.k_tiles; }
+    // rows of A/C are those of the CTA's rank, the B tile is B1 for rank 0 and B2 for rank 1
+    __device__ static Work get(const Params& p, int tile, uint32_t rank, int& /*cursor*/) {
+        const int m_pairs = p.m_tiles / 2;
+        const int m_pair = tile % m_pairs;
+        const int t = tile / m_pairs;
+        const int n_blk = t % p.n_tiles;
+        const int b = t / p.n_tiles;
+        const int m_blk = 2 * m_pair + static_cast<int>(rank);
+        Work w;
+        w.map_a = &p.map_a;
+        w.map_blo = rank == 0 ? static_cast<const void*>(&p.map_b1) : static_cast<const void*>(&p.map_b2);
+        w.map_bhi = w.map_blo;
+        w.a_row = m_blk * kTileM;
+        w.blo_row = w.bhi_row = n_blk * 128;
+        w.batch = b;
+        const long long sf_row = static_cast<long long>(p.sf_k_atoms) * kSfAtomBytes;
+        w.sfa = p.sfa + b * p.sfa_batch + m_blk * sf_row;
+        w.sfblo = p.sfb1 + b * p.sfb_batch + n_blk * sf_row;
+        w.sfbhi = p.sfb2 + b * p.sfb_batch + n_blk * sf_row;
+        w.ldc = p.ldc;
+        w.c = p.c + b * p.c_batch + static_cast<long long>(m_blk) * kTileM * p.ldc + n_blk * 128;
+        w.rows_valid = kTileM;
+        w.cols_valid = 128;
+        w.k_tile_begin = 0;
+        w.k_tile_count = p.k_tiles;
+        w.group = 0;
+        w.tile = tile;
+        w.split = 0;
+        return w;
+    }
+};
+
+// Grouped: the host fills GroupEntry::m_tiles with the number of 256-row pair tiles
+// and n_tiles with n / 256; tiles are walked m-fastest inside a group like in the
+// one-CTA kernel, `cursor` remembers the group of the previous tile.
+struct PairGrouped {
+    using Params = GroupedProblem;
+    static constexpr bool kGrouped = true;
+    __device__ static int total(const Params& p) { return p.total_tiles; }
+    __device__ static const GroupEntry* find(const Params& p, int tile, int& cursor) {
+        int g = cursor;
+        const GroupEntry* e = p.groups + g;
+        while (g + 1 < p.num_groups && tile >= e->tile_begin + e->m_tiles * e->n_tiles) {
+            ++g;
+            ++e;
+        }
+        cursor = g;
+        return e;
+    }
+    __device__ static int k_tiles(const Params& p, int tile, int& cursor) { return find(p, tile, cursor)->k_tiles; }
+    __device__ static Work get(const Params& p, int tile, uint32_t rank, int& cursor) {
+        const GroupEntry* e = find(p, tile, cursor);
+        const int local = tile - e->tile_begin;
+        const int m_pair = local % e->m_tiles;
+        const int n_blk = local / e->m_tiles;              // 256 columns
+        const int m_blk = 2 * m_pair + static_cast<int>(rank);
+        Work w;
+        w.map_a = &e->map_a;
+        w.map_blo = w.map_bhi = &e->map_b;
+        w.a_row = m_blk * kTileM;                          // may lie past the group's rows: TMA fills zeros
+        w.blo_row = w.bhi_row = n_blk * 256 + static_cast<int>(rank) * 128;
+        w.batch = 0;
+        const long long sf_row = static_cast<long long>(e->sf_k_atoms) * kSfAtomBytes;
+        const int sfa_blocks = (e->m + kTileM - 1) / kTileM;   // the buffer is padded to whole 128-row blocks
+        w.sfa = e->sfa + (m_blk < sfa_blocks ? m_blk : 0) * sf_row;
+        w.sfblo = e->sfb + (2 * n_blk) * sf_row;
+        w.sfbhi = e->sfb + (2 * n_blk + 1) * sf_row;
+        w.ldc = e->ldc;
+        w.c = e->c + static_cast<long long>(m_blk) * kTileM * e->ldc + n_blk * 256;
+        const int left = e->m - m_blk * kTileM;
+        w.rows_valid = left < 0 ? 0 : (left > kTileM ? kTileM : left);
+        w.cols_valid = 256;
+        w.k_tile_begin = 0;
+        w.k_tile_count = e->k_tiles;
+        w.group = cursor;
+        w.tile = tile;
+        w.split = 0;
+        return w;
+    }
+};
+
+// Grouped epilogue of one warp: 32 rows x 256 columns of fp16, no activation.  The
+// accumulator columns shared with the other buffer are fetched first and the buffer is
+// handed back; then 64 columns at a time go through a 4 KB staging box (128-byte-swizzle
+// layout) so that the global stores are whole 128-byte lines: one instruction writes
+// four rows x 128 bytes instead of 32 rows x 16 bytes.  Rows past the group's M are
+// predicated off.
+template <int kBuf>
+__device__ __forceinline__ void epilogue_tile_grouped_pair(const Work& w, uint32_t tmem_base, int quad, int lane,
+                                                           uint32_t release_bar, uint32_t staging, bool store) {
+    using TM = TmemMap<Mode::Group256>;
+    constexpr int kEarly = TM::kEarlyChunks;
+    constexpr int kSharedRel = (kBuf == 0) ? TM::kSharedBegin : 0;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
+    uint32_t early[kEarly][16];
+    static_assert(kEarly == 9, "the shared columns are fetched as 64 + 64 + 16");
+    tc_ld_x64(acc + kSharedRel, &early[0][0]);
+    tc_ld_x64(acc + kSharedRel + 64, &early[4][0]);
+    tc_ld_x16(acc + kSharedRel + 128, early[8]);
+    tc_wait_ld();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster_relaxed(release_bar);   // barrier of the pair's first CTA
+    const int rows_here = w.rows_valid - quad * 32;            // rows of this warp that exist
+    const uint32_t wr_base = staging + lane * 128;
+    const uint32_t swz = static_cast<uint32_t>(lane & 7);
+    __half* out = w.c + static_cast<long long>(quad * 32) * w.ldc;
+#pragma unroll
+    for (int chunk = 0; chunk < 16; ++chunk) {
+        const int col = chunk * 16;
+        const bool is_early = col >= kSharedRel && col < kSharedRel + kEarly * 16;
+        uint32_t x[16];
+        if (!is_early) {
+            tc_ld_x16(acc + col, x);
+            tc_wait_ld();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = early[(col - kSharedRel) / 16][i];
+        }
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) packed[i] = pack_half2(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
+        const uint32_t u0 = static_cast<uint32_t>((chunk & 3) * 2);
+        st_shared_v4(wr_base + ((u0 ^ swz) << 4), packed[0], packed[1], packed[2], packed[3]);
+        st_shared_v4(wr_base + (((u0 + 1) ^ swz) << 4), packed[4], packed[5], packed[6], packed[7]);
+        if ((chunk & 3) == 3) {
+            __syncwarp();
+            // lane l: 16-byte unit l % 8 of rows 4j + l / 8
+            const int unit = lane & 7;
+            __half* dst = out + (chunk >> 2) * 64 + unit * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int r = 4 * j + (lane >> 3);
+                uint32_t a, b, c, d;
+                ld_shared_v4(staging + r * 128 + ((static_cast<uint32_t>(unit) ^ static_cast<uint32_t>(r & 7)) << 4), a, b,
+                             c, d);
+                if (store && r < rows_here) st_global_v4(dst + static_cast<long long>(r) * w.ldc, a, b, c, d);
+            }
+            __syncwarp();
+        }
+    }
 }
 
+template <typename S>
 __global__ void __launch_bounds__(320, 1)
-nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
-    using TM = TmemMap<Mode::Dual>;
+nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
+    using TM = TmemMap<Mode::Dual>;          // same TMEM map for both: 256 accumulator columns per buffer
     using T = ModeTraits<Mode::Dual>;
+    static_assert(TmemMap<Mode::Group256>::kAccStride == TM::kAccStride, "one TMEM map for both pair kernels");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     ControlBlock* ctl = reinterpret_cast<ControlBlock*>(smem_raw + (smem_base - smem_u32(smem_raw)) +
@@ -88,7 +210,7 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
     const uint32_t rank = cluster_cta_rank();          // 0: issues the MMAs, 1: partner
     const int pair = blockIdx.x >> 1;
     const int pairs = gridDim.x >> 1;
-    const int total = (p.m_tiles / 2) * p.n_tiles * p.batches;
+    const int total = S::total(p);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPairStages; ++s) {
@@ -126,8 +248,10 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
         uint32_t s = 0, ph = 0, kt = 0, buf = 0, units = 0, retired = 0, rs = 0, rph = 0;
         bool ok = true;
         Tracer trace(nullptr, 0);
+        int cursor = 0;
         for (int tile = pair; ok && tile < total; tile += pairs) {
-            for (int i = 0; ok && i < p.k_tiles; ++i) {
+            const int k_tiles = S::k_tiles(p, tile, cursor);
+            for (int i = 0; ok && i < k_tiles; ++i) {
                 if (!mbar_wait<true>(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusSfWait)) {
                     ok = false;
                     break;
@@ -190,9 +314,15 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
             Tracer trace(nullptr, 0);
+            int cursor = 0, last_group = -1;
             for (int tile = pair; ok && tile < total; tile += pairs) {
-                const Work w = pair_work(p, tile, rank);
-                for (int i = 0; i < p.k_tiles; ++i) {
+                const Work w = S::get(p, tile, rank, cursor);
+                if (S::kGrouped && w.group != last_group) {   // tensor maps of a new group, written by the host
+                    tensormap_acquire(w.map_a);
+                    tensormap_acquire(w.map_blo);
+                    last_group = w.group;
+                }
+                for (int i = 0; i < w.k_tile_count; ++i) {
                     if (!mbar_wait<true>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
                                                  kStatusProducerWait)) {
                         ok = false;
@@ -233,7 +363,9 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             bool failed = false;
             Tracer trace(p.trace, 0);
             const long long kernel_t0 = clock64();
+            int cursor = 0;
             for (int tile = pair; tile < total && !failed; tile += pairs, ++it) {
+                const int k_tiles = S::k_tiles(p, tile, cursor);
                 trace(8);
                 // the first k-tile's scale factors are normally in place long before the
                 // accumulator comes back: pass that barrier first, off the hand-back path
@@ -253,7 +385,7 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
                 trace(9);   // accumulator buffer available
                 const uint32_t acc_addr = tmem_base + (it & 1) * TM::kAccStride;
 #pragma unroll 1
-                for (int i = 0; i < p.k_tiles; ++i) {
+                for (int i = 0; i < k_tiles; ++i) {
                     // eight arrivals: both CTAs' scale factors are in TMEM; the arriving warps
                     // waited for their CTA's operands first
                     if (i > 0) {
@@ -291,10 +423,10 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
         __syncwarp();
     } else if (warp < 4) {
         // ------------------------------ epilogue (each CTA its own 128 rows)
-        int it = 0;
+        int it = 0, cursor = 0;
         Tracer trace(lane == 0 && blockIdx.x == 0 ? p.trace : nullptr, warp == 0 ? 7 : warp);
         for (int tile = pair; tile < total; tile += pairs, ++it) {
-            const Work w = pair_work(p, tile, rank);
+            const Work w = S::get(p, tile, rank, cursor);
             const uint32_t release_bar = map_to_cta(smem_u32(&ctl->acc_release[it & 1]), 0);
             if (!mbar_wait<true>(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
                                  kStatusEpilogueWait))
@@ -303,15 +435,24 @@ nvfp4_dual_gemm_pair(const __grid_constant__ DenseProblem p, int flags) {
             trace(1);   // accumulator complete
             const bool store = !(flags & kFlagSkipStores);   // timing probe
             const uint32_t staging = staging_base + static_cast<uint32_t>(warp) * 8192u;
-            const int c_col = w.blo_row, c_row = w.a_row + warp * 32;
-            if (it & 1)
-                epilogue_tile_staged<1>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store, &trace);
-            else
-                epilogue_tile_staged<0>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store, &trace);
+            if constexpr (S::kGrouped) {
+                if (it & 1)
+                    epilogue_tile_grouped_pair<1>(w, tmem_base, warp, lane, release_bar, staging, store);
+                else
+                    epilogue_tile_grouped_pair<0>(w, tmem_base, warp, lane, release_bar, staging, store);
+            } else {
+                const int c_col = w.blo_row, c_row = w.a_row + warp * 32;
+                if (it & 1)
+                    epilogue_tile_staged<1>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store,
+                                            &trace);
+                else
+                    epilogue_tile_staged<0>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store,
+                                            &trace);
+            }
             trace(2);   // tile stored
             tc_fence_before_sync();
         }
-        if (lane == 0) bulk_wait_group_all();   // the last boxes are in global memory before the CTA exits
+        if (!S::kGrouped && lane == 0) bulk_wait_group_all();   // the last boxes have reached global memory
         __syncwarp();
     }
     // Nobody leaves while the partner may still signal its barriers or while MMAs

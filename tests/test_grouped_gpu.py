@@ -6,7 +6,7 @@ pytestmark = pytest.mark.gpu
 
 TOL_NORTH_STAR = 1e-2
 TOL_REFERENCE = 1e-3
-V_AUTO, V_PERSISTENT, V_SERIAL = 0, 1, 2
+V_AUTO, V_PERSISTENT, V_SERIAL, V_PAIR = 0, 1, 2, 5
 
 # utils/group_gemm/task.yml:47-56 (seed 1111)
 REFERENCE_TESTS = [
@@ -57,6 +57,58 @@ def test_tile_widths(pkg, oracle, tile_n, variant):
     m, n, k = [200, 64, 384], [512, 384, 256], [512, 256, 768]
     data = pkg.inputs.generate_grouped_input(m, n, k, 3, 5, dist="uniform16", device="cuda")
     _check(oracle, data, _run(pkg, data, variant, tile_n), TOL_NORTH_STAR)
+
+
+# CTA pairs (256 x 256 tiles): one tile, a group smaller than one CTA's rows, empty groups,
+# ragged counts around the 128- and 256-row boundaries, several tiles per pair
+PAIR_LISTS = [
+    ([256], [256], [256]),
+    ([96], [256], [512]),
+    ([300, 0, 72], [256, 512, 256], [256, 512, 768]),
+    ([40, 56, 384, 512], [512, 256, 256, 256], [256, 256, 256, 256]),
+    ([1000, 513, 257, 255], [512, 256, 768, 256], [512, 1024, 256, 512]),
+]
+
+
+@pytest.mark.parametrize("case", range(len(PAIR_LISTS)))
+@pytest.mark.parametrize("dist,tol", [("reference", TOL_REFERENCE), ("uniform16", TOL_NORTH_STAR)])
+def test_cta_pair_variant(pkg, oracle, case, dist, tol):
+    m, n, k = PAIR_LISTS[case]
+    data = pkg.inputs.generate_grouped_input(m, n, k, len(m), 7, dist=dist, device="cuda")
+    out = [o.clone() for o in _run(pkg, data, V_PAIR)]
+    _check(oracle, data, out, tol)
+    # same MMAs in the same k order as the one-CTA kernel
+    one_cta = _run(pkg, data, V_PERSISTENT)
+    for o, w in zip(out, one_cta):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16))
+
+
+def test_cta_pair_leaves_rows_beyond_m_alone(pkg):
+    m, n, k = 72, 256, 256
+    data = pkg.inputs.generate_grouped_input([m], [n], [k], 1, 2, dist="reference", device="cuda")
+    (a, b, _c) = data[0][0]
+    big = torch.full((384, n, 1), 7.0, dtype=torch.float16, device="cuda")
+    data[0][0] = (a, b, big[:m])
+    pkg.group_gemm.custom_kernel(data, variant=V_PAIR)
+    torch.cuda.synchronize()
+    assert torch.all(big[m:] == 7.0)
+    assert not torch.all(big[:m] == 7.0)
+
+
+def test_cta_pair_needs_n_multiple_of_256(pkg):
+    data = pkg.inputs.generate_grouped_input([64], [384], [256], 1, 0, device="cuda")
+    with pytest.raises(ValueError, match="256"):
+        pkg.group_gemm.custom_kernel(data, variant=V_PAIR)
+
+
+def test_large_list_takes_the_pair_kernel_by_default(pkg, oracle):
+    # 8 groups x (4 x 4) pair tiles >= one per SM: AUTO and PAIR must agree bit for bit
+    m = [1000, 1024, 900, 777, 1024, 513, 1024, 960]
+    data = pkg.inputs.generate_grouped_input(m, [1024] * 8, [256] * 8, 8, 5, dist="reference", device="cuda")
+    auto = [o.clone() for o in _run(pkg, data)]
+    _check(oracle, data, auto, TOL_REFERENCE)
+    for o, w in zip(auto, _run(pkg, data, V_PAIR)):
+        assert torch.equal(o.view(torch.int16), w.view(torch.int16))
 
 
 def test_empty_groups_are_skipped(pkg, oracle):
