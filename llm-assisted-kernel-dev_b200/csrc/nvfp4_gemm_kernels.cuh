@@ -249,8 +249,8 @@ template <Mode M> struct StageLayout {
 };
 
 // TMEM columns (512 per SM).
-// N=256 accumulators: two buffers at columns 0 and 128 that share columns
-// [128,256); the epilogue first pulls the shared columns into registers and
+// N=256 accumulators: two buffers at columns 0 and 112 that share columns
+// [112,256); the epilogue first pulls the shared columns into registers and
 // hands them back, so the next tile's MMAs overlap with the rest of the epilogue.
 // N=128 accumulators: two disjoint buffers at 0 and 128.
 // Scale factors: a ring of slots, one per 64-k block (SFA 4 columns + SFB
@@ -262,7 +262,8 @@ template <Mode M> struct StageLayout {
 // so copying through the tensor pipe caps it near half of its peak; the serial
 // bring-up kernel still uses tcgen05.cp.  The ring must cover the latency of the
 // hand-back loop (MMA retires -> commit seen by the scale-factor warps -> store
-// -> MMA warp sees the arrival, about 500 cycles): it holds 2.5 k-tiles.
+// -> MMA warp sees the arrival, 500-1000 cycles): it holds three k-tiles (with 2.5 the
+// writers of k-tile j had to wait for the MMAs of k-tile j-2).
 template <Mode M> struct TmemMap {
     using T = ModeTraits<M>;
     static constexpr bool kOverlapped = (T::kMmaN == 256);
@@ -378,11 +379,11 @@ __device__ __forceinline__ void store_chunk(__half* row_ptr, int chunk, const ui
 }
 
 // Epilogue of one tile for one warp (TMEM lane quadrant `quad`).  When the
-// accumulator buffers overlap, the 96 shared columns are pulled into registers
+// accumulator buffers overlap, the 144 shared columns are pulled into registers
 // first and `release` is signalled before any math; their partner columns (the
 // other product of the dual GEMM) are not shared and are read later.
-//   buffer 0 (columns 0-255):   shared = its columns 128-255
-//   buffer 1 (columns 128-383): shared = its columns 0-127
+//   buffer 0 (columns 0-255):   shared = its columns 112-255
+//   buffer 1 (columns 112-367): shared = its columns 0-143
 template <Mode M, int kBuf, bool kReleaseInCluster = false>
 __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base, int quad, int lane,
                                               uint32_t release_bar, bool store = true) {

@@ -106,6 +106,9 @@ def test_grouped_argument_errors(pkg):
     assert _grouped(lib, [(64, 128, 256)] * 3, ws_bytes=100) == E.E_WORKSPACE
     assert _grouped(lib, [(64, 128, 256)], tile_n=192) == E.E_VARIANT
     assert _grouped(lib, [(64, 128, 256)], variant=7) == E.E_VARIANT
+    # CTA pairs work on 256-column tiles
+    assert _grouped(lib, [(64, 256, 256), (64, 384, 256)], variant=E.VARIANT_PAIR) == E.E_SHAPE
+    assert "256" in lib.b200_last_error().decode()
     flat = (ctypes.c_int * 3)(1, 128, 256)
     assert lib.b200_grouped_gemm_nvfp4(0, None, None, None, None, None, flat, FAKE, 0, None, 0, None) == E.E_SHAPE
     # a NULL pointer is fine for an empty group, and all-empty input is a no-op that needs no GPU
