@@ -452,7 +452,9 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
             trace(2);   // tile stored
             tc_fence_before_sync();
         }
-        if (!S::kGrouped && lane == 0) bulk_wait_group_all();   // the last boxes have reached global memory
+        // the staging area must outlive the TMA unit's reads; the stores themselves are
+        // complete at the latest when the grid is
+        if (!S::kGrouped && lane == 0) bulk_wait_group_read_all();
         __syncwarp();
     }
     // Nobody leaves while the partner may still signal its barriers or while MMAs
