@@ -195,6 +195,30 @@ def time_launches(torch, fn, steps, warmup, barrier):
     return start.elapsed_time(stop) / 1e3, t0, t1
 
 
+def run_grouped_only(args):
+    """`--grouped g8|moe`: warm-up + timed launches of one grouped list and nothing else."""
+    import torch
+    pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
+    device = "cuda:0"
+    torch.cuda.set_device(0)
+    if args.grouped == "g8":
+        ms = pkg.inputs.uniform_group_rows(8, seed=0)
+        data = pkg.inputs.generate_grouped_input(ms, [4096] * 8, [7168] * 8, 8, 0, dist="uniform16", device=device)
+    else:
+        ms = pkg.inputs.moe_expert_counts(8192, 64, 8, seed=0)
+        data = pkg.inputs.generate_grouped_input(ms, [2048] * 64, [7168] * 64, 64, 0, dist="uniform16", device=device)
+    launches0 = pkg._lib.launch_count()
+    sec, _, _ = time_launches(torch, lambda i: pkg.group_gemm.custom_kernel(data), args.steps, args.warmup, lambda: None)
+    status = pkg._lib.read_status(0)
+    if status:
+        raise SystemExit(f"device status word {status:#x}: an on-device wait timed out")
+    flops = pkg.formats.grouped_gemm_flops(data[3])
+    print(json.dumps({"workload": "grouped_" + args.grouped, "us_per_launch": sec / args.steps * 1e6,
+                      "tflops": flops * args.steps / sec / 1e12, "steps": args.steps, "warmup": args.warmup,
+                      "gpu_launches": int(pkg._lib.launch_count() - launches0 - args.warmup),
+                      "note": "grouped-only run for profiler captures"}), flush=True)
+
+
 def run_extra(torch, pkg, device, peaks, steps, warmup):
     """Other benchmark configurations, one GPU: microseconds per launch."""
     extra = {}
@@ -422,6 +446,8 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-timed launches (no e2e, CPU baseline or extras): for profiler captures")
     ap.add_argument("--shape", default=None, help="M,N,K override of the dual-GEMM shape (profiler captures)")
+    ap.add_argument("--grouped", default=None, choices=["g8", "moe"],
+                    help="launch only the G=8 or the 64-expert grouped GEMM (profiler captures, one GPU)")
     args = ap.parse_args()
     if args.shape:
         global M, N, K, WORKLOAD
@@ -430,6 +456,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.grouped:
+        run_grouped_only(args)
     else:
         run_ours(args)
 
