@@ -550,9 +550,10 @@ __device__ __forceinline__ bool epilogue_tile_splitk(const DenseProblem& p, cons
     __threadfence();
     epilogue_bar_sync();
     if (threadIdx.x == 0) st_release_gpu_u32(flags + w.split, p.splitk_epoch);
-    // ---- wait for the peers (lane 0 polls; bounded)
-    uint32_t ok = 1;
-    if (lane == 0) {
+    // ---- wait for the peers (every lane polls: a single polling lane followed by a
+    // shuffle wakes the warp up measurably later; bounded)
+    bool ok = true;
+    {
         const long long t0 = clock64();
         for (int peer = 0; peer < splits && ok; ++peer) {
             if (peer == w.split) continue;
@@ -560,13 +561,13 @@ __device__ __forceinline__ bool epilogue_tile_splitk(const DenseProblem& p, cons
                 if (*abort_flag || clock64() - t0 > kWaitTimeoutCycles) {
                     *abort_flag = 1u;
                     atomicOr(p.status, kStatusSplitKWait);
-                    ok = 0;
+                    ok = false;
                     break;
                 }
             }
         }
     }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
+    ok = __all_sync(0xffffffffu, ok);
     if (ok) {
         __half* row_ptr = w.c + static_cast<long long>(row) * w.ldc;
 #pragma unroll 1
@@ -605,7 +606,7 @@ __device__ __forceinline__ bool epilogue_tile_splitk(const DenseProblem& p, cons
     tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(release_bar);       // accumulator drained: the MMA warp may reuse it
-    return ok != 0;
+    return ok;
 }
 
 // ---------------------------------------------------------------------------
