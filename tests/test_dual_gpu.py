@@ -164,3 +164,19 @@ def test_large_shape_properties(pkg):
     # (2) determinism: a second run is bit-identical
     out2 = _run(pkg, data, V_AUTO)
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+
+
+def test_pair_kernel_is_deterministic_over_many_launches(pkg):
+    # alternating shapes back to back: every launch must reproduce its first result bit for bit
+    # and leave the device status word clear (a lost hand-over would time out or change bits)
+    shapes = [(512, 2048, 1024), (256, 128, 4096), (1024, 4864, 256)]
+    inputs = [pkg.inputs.generate_input(m, n, k, 1, 11 + i, dist="uniform16", device="cuda")
+              for i, (m, n, k) in enumerate(shapes)]
+    first = [_run(pkg, d, V_PAIR).clone() for d in inputs]
+    for rep in range(40):
+        for d, want in zip(inputs, first):
+            out = pkg.dual_gemm.custom_kernel(d, variant=V_PAIR)
+        torch.cuda.synchronize()
+        assert pkg._lib.read_status(0) == 0
+        for d, want in zip(inputs, first):
+            assert torch.equal(d[9].view(torch.int16), want.view(torch.int16)), rep

@@ -178,3 +178,19 @@ def test_repeated_calls_reuse_descriptors(pkg, oracle):
     other = pkg.inputs.generate_grouped_input(m, n, k, 2, 1153, dist="reference", device="cuda")
     _check(oracle, other, _run(pkg, other), TOL_REFERENCE)
     _check(oracle, data, _run(pkg, data), TOL_REFERENCE)
+
+
+def test_pair_kernel_is_deterministic_over_many_launches(pkg):
+    lists = [([300, 0, 72, 1000], [256, 512, 256, 512], [256, 512, 768, 256]),
+             ([129, 255, 257], [1024, 256, 512], [512, 1024, 256])]
+    inputs = [pkg.inputs.generate_grouped_input(m, n, k, len(m), 3 + i, dist="uniform16", device="cuda")
+              for i, (m, n, k) in enumerate(lists)]
+    first = [[o.clone() for o in _run(pkg, d, V_PAIR)] for d in inputs]
+    for rep in range(40):
+        for d in inputs:
+            pkg.group_gemm.custom_kernel(d, variant=V_PAIR)
+        torch.cuda.synchronize()
+        assert pkg._lib.read_status(torch.cuda.current_device()) == 0
+        for d, want in zip(inputs, first):
+            for (_a, _b, c), w in zip(d[0], want):
+                assert torch.equal(c.view(torch.int16), w.view(torch.int16)), rep
