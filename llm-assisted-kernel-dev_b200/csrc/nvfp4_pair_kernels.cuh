@@ -352,7 +352,9 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         __syncwarp();
     } else if (warp == 4) {
         // ------------------------------ MMA issuer (first CTA of the pair only)
-        if (lane == 0 && rank == 0) {
+        // The whole warp runs the loop in lock step (waits included) so that descriptors and
+        // addresses are warp-uniform values; one elected lane issues each MMA and commit.
+        if (rank == 0) {
             constexpr uint32_t kUnitCols = TM::kGranule * TM::kSlotCols;
             const uint32_t desc_lo_base = smem_desc_lo(smem_base + PairStage::kOffA);
             const uint32_t sf_ready_bar = smem_u32(&ctl->sf_ready[0]);
@@ -361,7 +363,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
             uint32_t s = 0, ph = 0, a_lo = desc_lo_base, buf = 0;
             int it = 0;
             bool failed = false;
-            Tracer trace(p.trace, 0);
+            Tracer trace(lane == 0 ? p.trace : nullptr, 0);
             const long long kernel_t0 = clock64();
             int cursor = 0;
             for (int tile = pair; tile < total && !failed; tile += pairs, ++it) {
@@ -369,14 +371,14 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 trace(8);
                 // the first k-tile's scale factors are normally in place long before the
                 // accumulator comes back: pass that barrier first, off the hand-back path
-                if (!mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull))) {
                     failed = true;
                     break;
                 }
                 if (it > 0) {
                     const int r = it - 1;
-                    if (!mbar_wait(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
-                                           kStatusMmaWaitAcc)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag,
+                                                           p.status, kStatusMmaWaitAcc))) {
                         failed = true;
                         break;
                     }
@@ -389,7 +391,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     // eight arrivals: both CTAs' scale factors are in TMEM; the arriving warps
                     // waited for their CTA's operands first
                     if (i > 0) {
-                        if (!mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull)) {
+                        if (!__all_sync(0xffffffffu, mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull))) {
                             failed = true;
                             break;
                         }
@@ -401,11 +403,11 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     for (int kb = 0; kb < kKBlocks; ++kb) {
                         if (kb > 0 && kb % TM::kGranule == 0) b = (b + 1 == TM::kBuffers) ? 0u : b + 1;
                         const uint32_t sfa = sf_base + b * kUnitCols + (kb % TM::kGranule) * TM::kSlotCols;
-                        tc_mma_mxf4nvf4_pair_lo(acc_addr, a_lo + 2 * kb, a_lo + (PairStage::kOffB >> 4) + 2 * kb,
-                                                idesc_mxf4nvf4(256, T::kMmaN), sfa, sfa + 4,
-                                                (kb > 0 || i > 0) ? 1u : 0u);
+                        tc_mma_mxf4nvf4_pair_lo_elect(acc_addr, a_lo + 2 * kb, a_lo + (PairStage::kOffB >> 4) + 2 * kb,
+                                                      idesc_mxf4nvf4(256, T::kMmaN), sfa, sfa + 4,
+                                                      (kb > 0 || i > 0) ? 1u : 0u);
                     }
-                    tc_commit_pair_both(empty_mine + s * 8, 3);   // both CTAs' `empty` barriers
+                    tc_commit_pair_both_elect(empty_mine + s * 8, 3);   // both CTAs' `empty` barriers
                     trace(2);   // k-tile issued
                     buf += kKBlocks / TM::kGranule;
                     if (buf >= static_cast<uint32_t>(TM::kBuffers)) buf -= TM::kBuffers;
@@ -414,11 +416,11 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     if (s == kPairStages) { s = 0; ph ^= 1u; a_lo = desc_lo_base; }
                 }
                 if (failed) break;
-                tc_commit_pair_both(smem_u32(&ctl->acc_full[it & 1]), 3);
+                tc_commit_pair_both_elect(smem_u32(&ctl->acc_full[it & 1]), 3);
             }
-            tc_commit_pair(smem_u32(&ctl->aux[0]));
+            tc_commit_pair_elect(smem_u32(&ctl->aux[0]));
             mbar_wait(smem_u32(&ctl->aux[0]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
-            if (p.trace && blockIdx.x == 0) p.trace[8 * 1024 - 1] = static_cast<unsigned long long>(clock64() - kernel_t0);
+            if (lane == 0 && p.trace && blockIdx.x == 0) p.trace[8 * 1024 - 1] = static_cast<unsigned long long>(clock64() - kernel_t0);
         }
         __syncwarp();
     } else if (warp < 4) {
