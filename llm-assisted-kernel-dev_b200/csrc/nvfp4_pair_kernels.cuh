@@ -371,13 +371,13 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 trace(8);
                 // the first k-tile's scale factors are normally in place long before the
                 // accumulator comes back: pass that barrier first, off the hand-back path
-                if (!__all_sync(0xffffffffu, mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull))) {
+                if (!__all_sync(0xffffffffu, mbar_wait<true>(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull))) {
                     failed = true;
                     break;
                 }
                 if (it > 0) {
                     const int r = it - 1;
-                    if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag,
+                    if (!__all_sync(0xffffffffu, mbar_wait<true>(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag,
                                                            p.status, kStatusMmaWaitAcc))) {
                         failed = true;
                         break;
@@ -391,7 +391,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     // eight arrivals: both CTAs' scale factors are in TMEM; the arriving warps
                     // waited for their CTA's operands first
                     if (i > 0) {
-                        if (!__all_sync(0xffffffffu, mbar_wait(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull))) {
+                        if (!__all_sync(0xffffffffu, mbar_wait<true>(sf_ready_bar + s * 8u, ph, abort_flag, p.status, kStatusMmaWaitFull))) {
                             failed = true;
                             break;
                         }
@@ -419,7 +419,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 tc_commit_pair_both_elect(smem_u32(&ctl->acc_full[it & 1]), 3);
             }
             tc_commit_pair_elect(smem_u32(&ctl->aux[0]));
-            mbar_wait(smem_u32(&ctl->aux[0]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
+            mbar_wait<true>(smem_u32(&ctl->aux[0]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
             if (lane == 0 && p.trace && blockIdx.x == 0) p.trace[8 * 1024 - 1] = static_cast<unsigned long long>(clock64() - kernel_t0);
         }
         __syncwarp();
