@@ -389,14 +389,22 @@ def run_ours(args):
             dist.destroy_process_group()
         return
 
-    fp4_peak = 4.0 * peaks["bf16_tflops"]
+    # Denominator: 4 x the measured cuBLAS bf16 rate (no FP4 figure is measured).  A long run of
+    # back-to-back launches is in the power-capped regime, like the "sustained" bf16 figure;
+    # a short one is compared with the burst figure.  Both fractions are reported.
+    sustained = sec > 0.2 and "sw_power_cap" in (clocks.get("reasons") or [])
+    peak_key = "bf16_tflops_sustained" if sustained else "bf16_tflops"
+    fp4_peak = 4.0 * peaks[peak_key]
     per_launch_flops = 4.0 * M * n_local * K
     achieved = per_launch_flops * args.steps / sec / 1e12     # this rank's kernel
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": fp4_peak, "unit": "TFLOP/s", "frac": achieved / fp4_peak,
-        "peak_basis": f"4 x {peaks['source']} cuBLAS bf16 burst ({peaks['bf16_tflops']} TFLOP/s): no measured FP4 "
-                      f"figure exists; nominal dense NVFP4 is {NOMINAL_FP4_TFLOPS:.0f}",
-        "frac_nominal": achieved / NOMINAL_FP4_TFLOPS, "kernel": "nvfp4_dual_gemm_pair",
+        "peak_basis": f"4 x {peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} "
+                      f"({peaks[peak_key]} TFLOP/s; timed region {sec:.2f} s, "
+                      f"{'power-capped' if sustained else 'not power-capped or short'}): no measured FP4 figure "
+                      f"exists; nominal dense NVFP4 is {NOMINAL_FP4_TFLOPS:.0f}",
+        "frac_of_burst_peak": achieved / (4.0 * peaks["bf16_tflops"]),
+        "frac_nominal": achieved / NOMINAL_FP4_TFLOPS, "kernel": "nvfp4_gemm_pair<PairDual>",
         "avg_launch_us": sec / args.steps * 1e6, "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
         "algorithmic_bytes": pkg.formats.dual_gemm_bytes(M, n_local, K),
     }
