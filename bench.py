@@ -244,6 +244,18 @@ def run_extra(torch, pkg, device, peaks, steps, warmup):
     extra["grouped_g8_n4096_k7168"] = {"us_per_launch": us, "m": ms, "tflops": flops / us / 1e6,
                                        "hbm_gbs": byts / us / 1e3, "frac_hbm_peak": byts / us / 1e3 / peaks["hbm_gbs"]}
     del gsets
+    # activation quantiser fp16 -> NVFP4 (HBM-bound): the benchmark's A shape (4 inputs, 268 MB > L2; at 67 MB
+    # per launch a kernel runs ~20 us and launch + ramp-up keep any streaming kernel near 3.8 TB/s) and a
+    # 512 MB input that shows the steady rate
+    for name, qm, qk, n_in in (("quantize_f16_m8192_k4096", 8192, 4096, 4), ("quantize_f16_m32768_k8192", 32768, 8192, 1)):
+        xs = [torch.randn(qm, qk, device=device, dtype=torch.float16) for _ in range(n_in)]
+        sec, _, _ = time_launches(torch, lambda i: pkg.quantize.quantize_nvfp4(xs[i % n_in]), steps * 2, warmup,
+                                  lambda: None)
+        us = sec / (steps * 2) * 1e6
+        qbytes = qm * qk * 2 + qm * qk // 2 + qm * qk // 16
+        extra[name] = {"us_per_launch": us, "hbm_gbs": qbytes / us / 1e3,
+                       "frac_hbm_peak": qbytes / us / 1e3 / peaks["hbm_gbs"]}
+        del xs
     # MoE grouped GEMM, 64 experts, 8192 tokens top-8 (sum M = 65536), N=2048, K=7168
     counts = pkg.inputs.moe_expert_counts(8192, 64, 8, seed=0)
     data = pkg.inputs.generate_grouped_input(counts, [2048] * 64, [7168] * 64, 64, 0, dist="uniform16", device=device)

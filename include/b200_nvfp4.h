@@ -170,6 +170,24 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
                                    const void* const* sfa, const void* const* sfb, void* const* c,
                                    const int* mnk, void* stream, int device, uint32_t* status);
 
+/*
+ * Activation quantiser: x [rows, k] fp16 or bf16 (row pitch ldx elements) ->
+ * NVFP4 operand in the layout the GEMM entry points above take as `a`:
+ *   q   [rows, k/2] packed e2m1, low nibble = even k
+ *   sf  e4m3 scale factors, one per 16 consecutive k, in the reordered layout
+ *       (ceil(rows/128), k/64, 32, 4, 4); b200_quantize_sf_bytes(rows, k) bytes;
+ *       rows of the last 128-row block past `rows` get zero scale factors
+ *   s = e4m3_rn_satfinite(max|x| / 6), q = e2m1_rn_satfinite(x * fp32(1 / s)) (0 when s == 0)
+ * The step before the GEMMs in an FFN.  No counterpart in the reference, which
+ * draws already-quantised operands (dual_gemm/reference.py:114-190).
+ *   k % 64 == 0 (the GEMMs need k % 256 == 0); ldx % 8 == 0; pointers 16-byte aligned.
+ */
+#define B200_DTYPE_F16 0
+#define B200_DTYPE_BF16 1
+size_t b200_quantize_sf_bytes(int rows, int k);
+int b200_quantize_nvfp4(const void* x, int dtype, int rows, int k, int64_t ldx, void* q, void* sf,
+                        void* stream, int device);
+
 /* Synchronise `stream`, copy the library-owned status word of `device` into
  * *out and clear it. */
 int b200_read_status(int device, void* stream, uint32_t* out);

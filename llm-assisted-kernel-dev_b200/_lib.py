@@ -17,6 +17,7 @@ VARIANT_AUTO, VARIANT_PERSISTENT, VARIANT_SERIAL, VARIANT_SERIAL_2MMA, VARIANT_S
 E_NULL, E_SHAPE, E_ALIGN, E_WORKSPACE, E_VARIANT, E_DRIVER, E_LIMIT = -1, -2, -3, -4, -5, -6, -7
 
 STATIC_MAX_GROUPS = 64
+DTYPE_F16, DTYPE_BF16 = 0, 1
 
 _vp = ctypes.c_void_p
 _i = ctypes.c_int
@@ -35,6 +36,8 @@ SIGNATURES = {
     "b200_grouped_gemm_nvfp4_ex": (_i, [_i] + [_vp] * 6 + [_vp, _sz, _i, _i, _vp, _i, _vp]),
     "b200_grouped_workspace_bytes": (_sz, [_i]),
     "b200_grouped_gemm_nvfp4_static": (_i, [_i] + [_vp] * 6 + [_vp, _i, _vp]),
+    "b200_quantize_sf_bytes": (_sz, [_i, _i]),
+    "b200_quantize_nvfp4": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp, _i]),
     "b200_read_status": (_i, [_i, _vp, _u32p]),
 }
 

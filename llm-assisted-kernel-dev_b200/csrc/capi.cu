@@ -12,6 +12,7 @@
 #include "../../include/b200_nvfp4.h"
 #include "nvfp4_gemm_kernels.cuh"
 #include "nvfp4_pair_kernels.cuh"
+#include "nvfp4_quantize.cuh"
 
 namespace b200 {
 namespace {
@@ -657,6 +658,49 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
     p.trace = nullptr;
     return tile_n == 256 ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s)
                          : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s);
+}
+
+size_t b200_quantize_sf_bytes(int rows, int k) {
+    if (rows <= 0 || k <= 0 || k % 64) return 0;
+    return static_cast<size_t>((rows + 127) / 128) * (k / 64) * 512;
+}
+
+int b200_quantize_nvfp4(const void* x, int dtype, int rows, int k, int64_t ldx, void* q, void* sf, void* stream,
+                        int device) {
+    if (!x || !q || !sf) return fail(B200_E_NULL, "quantize: NULL tensor pointer");
+    if (dtype != B200_DTYPE_F16 && dtype != B200_DTYPE_BF16)
+        return fail(B200_E_VARIANT, "quantize: dtype %d is neither B200_DTYPE_F16 nor B200_DTYPE_BF16", dtype);
+    if (rows <= 0 || k <= 0) return fail(B200_E_SHAPE, "quantize: rows and k must be positive (got %d %d)", rows, k);
+    if (k % 64) return fail(B200_E_SHAPE, "quantize: k=%d is not a multiple of 64", k);
+    if (ldx < k || ldx % 8) return fail(B200_E_ALIGN, "quantize: ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
+    if (!aligned16(x) || !aligned16(q) || !aligned16(sf))
+        return fail(B200_E_ALIGN, "quantize: every tensor pointer must be 16-byte aligned");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    int rc;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+    const long long chunks = static_cast<long long>((rows + 127) / 128 * 128) * ((k / 16 + 31) / 32);
+    long long blocks = (chunks + 7) / 8;                       // eight warps per block
+    const long long cap = static_cast<long long>(st->sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint16_t* src = static_cast<const uint16_t*>(x);
+    const bool wide = (reinterpret_cast<uintptr_t>(x) % 32 == 0) && (ldx % 16 == 0);
+    const unsigned grid = static_cast<unsigned>(blocks);
+    uint8_t* qp = static_cast<uint8_t*>(q);
+    uint8_t* sfp = static_cast<uint8_t*>(sf);
+    if (dtype == B200_DTYPE_F16) {
+        if (wide) nvfp4_quantize<kQuantDtypeF16, true><<<grid, 256, 0, s>>>(src, ldx, qp, sfp, rows, k);
+        else nvfp4_quantize<kQuantDtypeF16, false><<<grid, 256, 0, s>>>(src, ldx, qp, sfp, rows, k);
+    } else {
+        if (wide) nvfp4_quantize<kQuantDtypeBF16, true><<<grid, 256, 0, s>>>(src, ldx, qp, sfp, rows, k);
+        else nvfp4_quantize<kQuantDtypeBF16, false><<<grid, 256, 0, s>>>(src, ldx, qp, sfp, rows, k);
+    }
+    B200_CUDA(cudaGetLastError());
+    ++g_launches;
+    return 0;
 }
 
 int b200_read_status(int device, void* stream, uint32_t* out) {

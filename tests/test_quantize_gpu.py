@@ -1,0 +1,92 @@
+"""GPU parity of the activation quantiser (fp16 / bf16 -> NVFP4) against the CPU
+restatement in oracle/, byte for byte, and its use as the GEMM's A operand."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _unpermute(oracle, sf_perm, rows, k):
+    return oracle.unpermute_sf(sf_perm.cpu(), rows, k // 16)[:, :, 0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,k", [(128, 256), (200, 512), (1, 64), (1000, 1792), (4096, 7168)])
+def test_matches_oracle_bit_for_bit(pkg, oracle, dtype, rows, k):
+    g = torch.Generator().manual_seed(rows * 31 + k)
+    x = (torch.randn(rows, k, generator=g) * torch.rand(rows, 1, generator=g) * 8).to(dtype)
+    q, sf_perm = pkg.quantize.quantize_nvfp4(x.cuda())
+    torch.cuda.synchronize()
+    want_q, want_sf = oracle.quantize_nvfp4(x)
+    assert torch.equal(q.view(torch.uint8).cpu()[:, :, 0], want_q)
+    assert torch.equal(_unpermute(oracle, sf_perm, rows, k), want_sf)
+    assert pkg.formats.is_kernel_sf_layout(sf_perm, rows, k, 1)
+
+
+def test_edge_values(pkg, oracle):
+    # zeros, negative zero, exact rounding ties, values that saturate the scale factor, tiny blocks
+    rows, k = 128, 256
+    x = torch.zeros(rows, k, dtype=torch.float16)
+    x[0, :16] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0])
+    x[1, :16] = 65504.0                      # amax / 6 > 448: the scale saturates, codes saturate at 6
+    x[2, :16] = -0.0
+    x[3, :16] = 6.0e-8                       # subnormal fp16: the scale rounds to zero, codes are zero
+    x[4, 16:32] = torch.linspace(-3, 3, 16)
+    x[5, :] = torch.arange(k, dtype=torch.float32).half() / 7
+    for dtype in (torch.float16, torch.bfloat16):
+        xd = x.to(dtype)
+        q, sf_perm = pkg.quantize.quantize_nvfp4(xd.cuda())
+        torch.cuda.synchronize()
+        want_q, want_sf = oracle.quantize_nvfp4(xd)
+        assert torch.equal(q.view(torch.uint8).cpu()[:, :, 0], want_q), dtype
+        assert torch.equal(_unpermute(oracle, sf_perm, rows, k), want_sf), dtype
+
+
+def test_padding_rows_get_zero_scale_factors(pkg):
+    rows, k = 72, 256
+    x = torch.randn(rows, k).half().cuda()
+    _q, sf_perm = pkg.quantize.quantize_nvfp4(x)
+    torch.cuda.synchronize()
+    raw = sf_perm.view(torch.uint8).cpu()        # (32, 4, 1, 4, 4, 1): row = a + 32 * b
+    row = torch.arange(32).view(32, 1) + 32 * torch.arange(4).view(1, 4)
+    assert torch.all(raw[:, :, 0, :, :, 0][row >= rows] == 0)
+    assert torch.any(raw[:, :, 0, :, :, 0][row < rows] != 0)
+
+
+def test_row_pitch_and_rejections(pkg, oracle):
+    big = torch.randn(64, 1024).half().cuda()
+    view = big[:, :512]                           # pitch 1024, k 512
+    q, sf_perm = pkg.quantize.quantize_nvfp4(view)
+    torch.cuda.synchronize()
+    want_q, want_sf = oracle.quantize_nvfp4(view.cpu())
+    assert torch.equal(q.view(torch.uint8).cpu()[:, :, 0], want_q)
+    assert torch.equal(_unpermute(oracle, sf_perm, 64, 512), want_sf)
+    # a view that is only 16-byte aligned with a pitch that is not a multiple of 32 bytes
+    odd = torch.randn(40, 520).half().cuda()[:, 8:8 + 256]
+    q, sf_perm = pkg.quantize.quantize_nvfp4(odd)
+    torch.cuda.synchronize()
+    want_q, want_sf = oracle.quantize_nvfp4(odd.cpu())
+    assert torch.equal(q.view(torch.uint8).cpu()[:, :, 0], want_q)
+    assert torch.equal(_unpermute(oracle, sf_perm, 40, 256), want_sf)
+    with pytest.raises(ValueError, match="64"):
+        pkg.quantize.quantize_nvfp4(torch.zeros(8, 48, dtype=torch.float16, device="cuda"))
+    with pytest.raises(ValueError):
+        pkg.quantize.quantize_nvfp4(torch.zeros(8, 64, dtype=torch.float32, device="cuda"))
+    with pytest.raises(ValueError):
+        pkg.quantize.quantize_nvfp4(torch.zeros(8, 64, dtype=torch.float16))
+
+
+def test_quantised_activations_feed_the_dual_gemm(pkg, oracle):
+    # quantise A on the GPU, keep the generator's B1/B2: the GEMM must agree with the oracle run on
+    # the oracle-quantised A (same bytes), i.e. the quantiser's output is a valid `a` / `sfa_perm`
+    m, n, k = 256, 256, 512
+    data = list(pkg.inputs.generate_input(m, n, k, 1, 5, dist="reference", device="cuda"))
+    x = (torch.randn(m, k, generator=torch.Generator().manual_seed(9)) * 0.5).half()
+    q, sf_perm = pkg.quantize.quantize_nvfp4(x.cuda())
+    data[0], data[6] = q, sf_perm
+    out = pkg.dual_gemm.custom_kernel(tuple(data))
+    torch.cuda.synchronize()
+    want_q, want_sf = oracle.quantize_nvfp4(x)
+    cpu = [t.cpu() if t is not None else None for t in data]
+    fp32 = oracle.dual_gemm_fp32(want_q.view(m, k // 2, 1), cpu[1], cpu[2], want_sf.view(m, k // 16, 1), cpu[4], cpu[5])
+    assert oracle.compare(out, fp32.to(torch.float16), 1e-3, 1e-3, expected_fp32=fp32) == []
