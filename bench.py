@@ -244,6 +244,14 @@ def run_extra(torch, pkg, device, peaks, steps, warmup):
     extra["grouped_g8_n4096_k7168"] = {"us_per_launch": us, "m": ms, "tflops": flops / us / 1e6,
                                        "hbm_gbs": byts / us / 1e3, "frac_hbm_peak": byts / us / 1e3 / peaks["hbm_gbs"]}
     del gsets
+    # the benchmark dual GEMM with its result re-quantised to NVFP4 in the epilogue (input of a down projection)
+    dq = pkg.inputs.generate_input(M, N, K, 1, 0, dist="uniform16", device=device)
+    sec, _, _ = time_launches(torch, lambda i: pkg.dual_gemm.dual_gemm_quantized(dq[0], dq[1], dq[2], dq[6], dq[7], dq[8]),
+                              steps, warmup, lambda: None)
+    us = sec / steps * 1e6
+    extra["dual_quantised_output_m8192_n14336_k4096"] = {"us_per_launch": us, "tflops": 4.0 * M * N * K / us / 1e6,
+                                                         "output_bytes": M * N // 2 + M * N // 16}
+    del dq
     # activation quantiser fp16 -> NVFP4 (HBM-bound): the benchmark's A shape (4 inputs, 268 MB > L2; at 67 MB
     # per launch a kernel runs ~20 us and launch + ramp-up keep any streaming kernel near 3.8 TB/s) and a
     # 512 MB input that shows the steady rate

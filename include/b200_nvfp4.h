@@ -171,6 +171,21 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
                                    const int* mnk, void* stream, int device, uint32_t* status);
 
 /*
+ * Dual GEMM with NVFP4 output: computes the same fp16 values as
+ * b200_dual_gemm_nvfp4 and re-quantises them in the epilogue like
+ * b200_quantize_nvfp4 would (byte for byte), so the result can be the `a` / `sfa`
+ * of the next block-scaled GEMM (the down projection of a SwiGLU FFN) without a
+ * round trip of fp16 C through memory.
+ *   q   [m, n/2] packed e2m1;  sf  reordered e4m3 scale factors of an [m, n]
+ *       operand, b200_quantize_sf_bytes(m, n) bytes
+ *   m % 256 == 0 (runs on the CTA-pair kernel), n % 128 == 0, k % 256 == 0, l = 1.
+ * No counterpart in the reference (its kernels store fp16, dual_gemm/submission.py:596-611).
+ */
+int b200_dual_gemm_nvfp4_quant(const void* a, const void* b1, const void* b2, const void* sfa,
+                               const void* sfb1, const void* sfb2, void* q, void* sf, int m, int n,
+                               int k, void* stream, int device, uint32_t* status);
+
+/*
  * Activation quantiser: x [rows, k] fp16 or bf16 (row pitch ldx elements) ->
  * NVFP4 operand in the layout the GEMM entry points above take as `a`:
  *   q   [rows, k/2] packed e2m1, low nibble = even k

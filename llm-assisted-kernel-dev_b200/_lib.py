@@ -36,6 +36,7 @@ SIGNATURES = {
     "b200_grouped_gemm_nvfp4_ex": (_i, [_i] + [_vp] * 6 + [_vp, _sz, _i, _i, _vp, _i, _vp]),
     "b200_grouped_workspace_bytes": (_sz, [_i]),
     "b200_grouped_gemm_nvfp4_static": (_i, [_i] + [_vp] * 6 + [_vp, _i, _vp]),
+    "b200_dual_gemm_nvfp4_quant": (_i, [_vp] * 8 + [_i] * 3 + [_vp, _i, _vp]),
     "b200_quantize_sf_bytes": (_sz, [_i, _i]),
     "b200_quantize_nvfp4": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp, _i]),
     "b200_read_status": (_i, [_i, _vp, _u32p]),

@@ -145,6 +145,7 @@ int device_state(int device, DeviceState** out) {
                               smem_bytes_persistent<Mode::Group256, kG256Stages>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDual>, kPairSmemBytes))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairGrouped>, kPairSmemBytes))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualQuant>, kPairSmemBytes))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Dual>, smem_bytes_serial<Mode::Dual>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group128>, smem_bytes_serial<Mode::Group128>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group256>, smem_bytes_serial<Mode::Group256>()))) return rc;
@@ -285,10 +286,14 @@ size_t b200_dual_splitk_workspace_bytes(int m, int n, int k, int l) {
     return splitk_bytes(tiles, splits);
 }
 
-int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
-                            const void* sfb2, void* c, int m, int n, int k, int l, int64_t ldc, int64_t c_batch,
-                            int64_t b_batch_bytes, int64_t sfb_batch_bytes, int variant, void* workspace,
-                            size_t workspace_bytes, void* stream, int device, uint32_t* status) {
+// Shared body of the dual-GEMM entry points.  q_out / sf_out non-NULL: the CTA-pair kernel
+// writes the re-quantised result there instead of fp16 to c (c is then unused).
+static int dual_gemm_impl(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
+                          const void* sfb2, void* c, int m, int n, int k, int l, int64_t ldc, int64_t c_batch,
+                          int64_t b_batch_bytes, int64_t sfb_batch_bytes, int variant, void* workspace,
+                          size_t workspace_bytes, void* stream, int device, uint32_t* status, void* q_out,
+                          void* sf_out) {
+    const bool quant = q_out != nullptr;
     if (c_batch == 0) c_batch = static_cast<int64_t>(m) * ldc;
     if (b_batch_bytes == 0) b_batch_bytes = static_cast<int64_t>(n) * (k / 2);
     if (sfb_batch_bytes == 0) sfb_batch_bytes = static_cast<int64_t>(n / 128) * (k / 64) * 512;
@@ -318,7 +323,7 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
         if ((rc = encode_operand_map(&fresh.a, a, m, k, l, static_cast<long long>(m) * (k / 2)))) return rc;
         if ((rc = encode_operand_map(&fresh.b1, b1, n, k, l, b_batch_bytes))) return rc;
         if ((rc = encode_operand_map(&fresh.b2, b2, n, k, l, b_batch_bytes))) return rc;
-        if ((rc = encode_output_map(&fresh.c, c, m, n, l, ldc, c_batch))) return rc;
+        if (!quant && (rc = encode_output_map(&fresh.c, c, m, n, l, ldc, c_batch))) return rc;
         if (g_dual_cache.size() >= 16) g_dual_cache.erase(g_dual_cache.begin());
         g_dual_cache.push_back(fresh);
         maps = &g_dual_cache.back();
@@ -331,6 +336,8 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
     p.sfb1 = static_cast<const uint8_t*>(sfb1);
     p.sfb2 = static_cast<const uint8_t*>(sfb2);
     p.c = static_cast<__half*>(c);
+    p.q_out = static_cast<uint8_t*>(q_out);
+    p.sf_out = static_cast<uint8_t*>(sf_out);
     p.ldc = ldc;
     p.c_batch = c_batch;
     p.sfa_batch = static_cast<long long>(m / 128) * (k / 64) * 512;
@@ -348,6 +355,7 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
                   ? static_cast<unsigned long long*>(workspace) : nullptr;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (quant) return launch_pair<PairDualQuant>(p, dual_pair_tiles(p), st->sm_count, 0, s);
     if (probe)
         return launch_persistent<Mode::Dual, kDualStages, DenseProblem, true>(p, p.total_tiles, st->sm_count,
                                                                               variant - B200_VARIANT_PROBE_BASE, s);
@@ -387,6 +395,27 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
         default:
             return launch_persistent<Mode::Dual, kDualStages>(p, p.total_tiles, st->sm_count, 0, s);
     }
+}
+
+int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
+                            const void* sfb2, void* c, int m, int n, int k, int l, int64_t ldc, int64_t c_batch,
+                            int64_t b_batch_bytes, int64_t sfb_batch_bytes, int variant, void* workspace,
+                            size_t workspace_bytes, void* stream, int device, uint32_t* status) {
+    return dual_gemm_impl(a, b1, b2, sfa, sfb1, sfb2, c, m, n, k, l, ldc, c_batch, b_batch_bytes, sfb_batch_bytes,
+                          variant, workspace, workspace_bytes, stream, device, status, nullptr, nullptr);
+}
+
+int b200_dual_gemm_nvfp4_quant(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
+                               const void* sfb2, void* q, void* sf, int m, int n, int k, void* stream, int device,
+                               uint32_t* status) {
+    if (!q || !sf) return fail(B200_E_NULL, "dual gemm (quantised output): NULL output pointer");
+    if (!aligned16(q) || !aligned16(sf))
+        return fail(B200_E_ALIGN, "dual gemm (quantised output): output pointers must be 16-byte aligned");
+    if (m > 0 && m % 256)
+        return fail(B200_E_SHAPE, "dual gemm (quantised output): m=%d is not a multiple of 256 (CTA-pair kernel)", m);
+    // `q` stands in for c in the shared argument checks (same alignment rule); it is never written as fp16
+    return dual_gemm_impl(a, b1, b2, sfa, sfb1, sfb2, q, m, n, k, 1, n, 0, 0, 0, B200_VARIANT_AUTO, nullptr, 0, stream,
+                          device, status, q, sf);
 }
 
 int b200_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,

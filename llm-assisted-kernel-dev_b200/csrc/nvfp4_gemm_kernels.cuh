@@ -97,6 +97,8 @@ struct alignas(64) DenseProblem {
     const uint8_t* sfb1;
     const uint8_t* sfb2;
     __half* c;
+    uint8_t* q_out;                      // quantised-output variant: packed e2m1 [m, n/2] instead of c ...
+    uint8_t* sf_out;                     // ... and its e4m3 scale factors in the reordered layout
     long long ldc, c_batch;              // elements
     long long sfa_batch, sfb_batch;      // bytes
     float* splitk_ws;                    // fp32 partial sums (split-k variant only)

@@ -27,6 +27,7 @@
 #pragma once
 
 #include "nvfp4_gemm_kernels.cuh"
+#include "nvfp4_quantize.cuh"
 
 namespace b200 {
 
@@ -49,6 +50,7 @@ constexpr uint32_t kStatusPairWait = 0x80;
 struct PairDual {
     using Params = DenseProblem;
     static constexpr bool kGrouped = false;
+    static constexpr bool kQuantOut = false;
     __device__ static int total(const Params& p) { return (p.m_tiles / 2) * p.n_tiles * p.batches; }
     __device__ static int k_tiles(const Params& p, int /*tile*/, int& /*cursor*/) { return p.k_tiles; }
     // rows of A/C are those of the CTA's rank, the B tile is B1 for rank 0 and B2 for rank 1
@@ -86,9 +88,16 @@ struct PairDual {
 // Grouped: the host fills GroupEntry::m_tiles with the number of 256-row pair tiles
 // and n_tiles with n / 256; tiles are walked m-fastest inside a group like in the
 // one-CTA kernel, `cursor` remembers the group of the previous tile.
+// Dual GEMM whose epilogue re-quantises its fp16 result to NVFP4 (packed e2m1 + e4m3
+// scale factors in the reordered layout), ready to be the A operand of the next GEMM.
+struct PairDualQuant : PairDual {
+    static constexpr bool kQuantOut = true;
+};
+
 struct PairGrouped {
     using Params = GroupedProblem;
     static constexpr bool kGrouped = true;
+    static constexpr bool kQuantOut = false;
     __device__ static int total(const Params& p) { return p.total_tiles; }
     __device__ static const GroupEntry* find(const Params& p, int tile, int& cursor) {
         int g = cursor;
@@ -190,6 +199,70 @@ __device__ __forceinline__ void epilogue_tile_grouped_pair(const Work& w, uint32
                 if (store && r < rows_here) st_global_v4(dst + static_cast<long long>(r) * w.ldc, a, b, c, d);
             }
             __syncwarp();
+        }
+    }
+}
+
+// Epilogue of the quantised-output dual GEMM for one warp (32 rows x 128 columns): the
+// fp16 value the plain kernel would store, silu(x) * y rounded to fp16, is quantised the
+// way nvfp4_quantize does it.  A lane holds one row and a 16-column chunk is exactly one
+// scale-factor block, so nothing crosses lanes: eight packed bytes per chunk go straight
+// to global memory and four chunks' scale bytes make one word of the reordered layout.
+// The result equals quantising the plain kernel's C byte for byte.
+template <int kBuf>
+__device__ __forceinline__ void epilogue_tile_quant(const DenseProblem& p, const Work& w, uint32_t tmem_base,
+                                                    int quad, int lane, uint32_t release_bar, int m_blk, int n_blk,
+                                                    bool store) {
+    using TM = TmemMap<Mode::Dual>;
+    constexpr int kEarly = TM::kEarlyChunks;
+    constexpr int kSharedRel = (kBuf == 0) ? TM::kSharedBegin : 0;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
+    uint32_t early[kEarly][16];
+    static_assert(kEarly == 9, "the shared columns are fetched as 64 + 64 + 16");
+    tc_ld_x64(acc + kSharedRel, &early[0][0]);
+    tc_ld_x64(acc + kSharedRel + 64, &early[4][0]);
+    tc_ld_x16(acc + kSharedRel + 128, early[8]);
+    tc_wait_ld();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster_relaxed(release_bar);   // barrier of the pair's first CTA
+    const int n_total = p.n_tiles * 128;
+    const long long row = static_cast<long long>(m_blk) * kTileM + quad * 32 + lane;
+    uint8_t* q_row = p.q_out + row * (n_total / 2) + n_blk * 64;
+    // scale factors of this row, columns n_blk*128 ...: k-blocks n_blk*8 + chunk of the (m, n/16) scale matrix
+    uint8_t* sf_row = p.sf_out + (static_cast<long long>(m_blk) * (n_total / 64) + n_blk * 2) * 512 + lane * 16 + quad * 4;
+    uint32_t sf_word = 0;
+#pragma unroll
+    for (int chunk = 0; chunk < 8; ++chunk) {
+        const int xcol = chunk * 16;
+        const int ycol = 128 + chunk * 16;
+        const bool x_early = xcol >= kSharedRel && xcol < kSharedRel + kEarly * 16;
+        const bool y_early = ycol >= kSharedRel && ycol < kSharedRel + kEarly * 16;
+        uint32_t x[16], y[16];
+        if (!x_early) tc_ld_x16(acc + xcol, x);
+        if (!y_early) tc_ld_x16(acc + ycol, y);
+        if (!x_early || !y_early) tc_wait_ld();
+        if (x_early) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = early[(xcol - kSharedRel) / 16][i];
+        }
+        if (y_early) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) y[i] = early[(ycol - kSharedRel) / 16][i];
+        }
+        uint32_t h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            h[i] = pack_half2(silu_mul(__uint_as_float(x[2 * i]), __uint_as_float(y[2 * i])),
+                              silu_mul(__uint_as_float(x[2 * i + 1]), __uint_as_float(y[2 * i + 1])));
+        uint2 packed;
+        const uint32_t sbyte = quantize_block<kQuantDtypeF16>(make_uint4(h[0], h[1], h[2], h[3]),
+                                                              make_uint4(h[4], h[5], h[6], h[7]), packed);
+        sf_word |= sbyte << (8 * (chunk & 3));
+        if (store) *reinterpret_cast<uint2*>(q_row + chunk * 8) = packed;
+        if ((chunk & 3) == 3) {
+            if (store) *reinterpret_cast<uint32_t*>(sf_row + (chunk >> 2) * 512) = sf_word;
+            sf_word = 0;
         }
     }
 }
@@ -437,7 +510,13 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
             trace(1);   // accumulator complete
             const bool store = !(flags & kFlagSkipStores);   // timing probe
             const uint32_t staging = staging_base + static_cast<uint32_t>(warp) * 8192u;
-            if constexpr (S::kGrouped) {
+            if constexpr (S::kQuantOut) {
+                const int m_blk = w.a_row / kTileM, n_blk = w.blo_row / 128;
+                if (it & 1)
+                    epilogue_tile_quant<1>(p, w, tmem_base, warp, lane, release_bar, m_blk, n_blk, store);
+                else
+                    epilogue_tile_quant<0>(p, w, tmem_base, warp, lane, release_bar, m_blk, n_blk, store);
+            } else if constexpr (S::kGrouped) {
                 if (it & 1)
                     epilogue_tile_grouped_pair<1>(w, tmem_base, warp, lane, release_bar, staging, store);
                 else
@@ -456,7 +535,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         }
         // the staging area must outlive the TMA unit's reads; the stores themselves are
         // complete at the latest when the grid is
-        if (!S::kGrouped && lane == 0) bulk_wait_group_read_all();
+        if (!S::kGrouped && !S::kQuantOut && lane == 0) bulk_wait_group_read_all();
         __syncwarp();
     }
     // Nobody leaves while the partner may still signal its barriers or while MMAs

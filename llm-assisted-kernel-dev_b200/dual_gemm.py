@@ -105,6 +105,33 @@ def dual_gemm(a, b1, b2, sfa_perm, sfb1_perm, sfb2_perm, c, *, variant: int = _l
     return c
 
 
+def dual_gemm_quantized(a, b1, b2, sfa_perm, sfb1_perm, sfb2_perm):
+    """``silu(A @ B1.T) * (A @ B2.T)`` re-quantised to NVFP4 in the epilogue:
+    returns ``(q, sf_perm)`` -- ``q`` [M, N/2, 1] packed e2m1 and the
+    (32, 4, M/128, 4, N/64, 1) e4m3 view of a fresh reordered scale-factor buffer --
+    equal byte for byte to ``quantize.quantize_nvfp4`` applied to the fp16 result of
+    ``dual_gemm``.  M % 256 == 0, L == 1.  The input of the next block-scaled GEMM
+    (the reference stores fp16: dual_gemm/submission.py:596-611)."""
+    from .formats import E4M3, FP4X2
+    if not a.is_cuda:
+        raise ValueError("dual_gemm_quantized needs CUDA tensors (there is no CPU path)")
+    m, n, k = a.shape[0], b1.shape[0], a.shape[1] * 2
+    if a.shape[2] != 1:
+        raise ValueError("dual_gemm_quantized supports l == 1 only")
+    for name, t, rows in (("sfa", sfa_perm, m), ("sfb1", sfb1_perm, n), ("sfb2", sfb2_perm, n)):
+        if not is_kernel_sf_layout(t, rows, k, 1):
+            raise ValueError(f"{name} is not in the (32,4,rest,4,K/64,L) reordered scale-factor layout")
+    lib = _lib.load()
+    q = torch.empty((m, n // 2), dtype=torch.uint8, device=a.device)
+    sf = torch.empty((1, max(m // 128, 1), max(n // 64, 1), 32, 4, 4), dtype=torch.uint8, device=a.device)
+    code = lib.b200_dual_gemm_nvfp4_quant(a.data_ptr(), b1.data_ptr(), b2.data_ptr(), sfa_perm.data_ptr(),
+                                          sfb1_perm.data_ptr(), sfb2_perm.data_ptr(), q.data_ptr(), sf.data_ptr(),
+                                          m, n, k, torch.cuda.current_stream(a.device).cuda_stream, a.device.index,
+                                          None)
+    _lib.check(code)
+    return q.view(m, n // 2, 1).view(FP4X2), sf.permute(3, 4, 1, 5, 2, 0).view(E4M3)
+
+
 def custom_kernel(data, *, variant: int = _lib.VARIANT_AUTO):
     """``custom_kernel(data) -> output``; ``data`` is the reference's
     ``(a, b1, b2, sfa, sfb1, sfb2, sfa_perm, sfb1_perm, sfb2_perm, c)``.

@@ -55,3 +55,14 @@ def test_entry_point_rejects_bad_arguments(pkg):
     assert lib.b200_quantize_sf_bytes(128, 256) == 2048
     assert lib.b200_quantize_sf_bytes(129, 256) == 4096
     assert lib.b200_quantize_sf_bytes(128, 100) == 0
+
+
+def test_quantised_output_entry_point_rejects_bad_arguments(pkg):
+    lib = pkg._lib.load()
+    E = pkg._lib
+    ptrs = [FAKE + 65536 * i for i in range(8)]
+    assert lib.b200_dual_gemm_nvfp4_quant(*ptrs, 128, 128, 256, None, 0, None) == E.E_SHAPE
+    assert "256" in lib.b200_last_error().decode()
+    assert lib.b200_dual_gemm_nvfp4_quant(*ptrs[:6], None, ptrs[7], 256, 128, 256, None, 0, None) == E.E_NULL
+    assert lib.b200_dual_gemm_nvfp4_quant(*ptrs[:7], FAKE + 4, 256, 128, 256, None, 0, None) == E.E_ALIGN
+    assert lib.b200_dual_gemm_nvfp4_quant(*ptrs, 256, 100, 256, None, 0, None) == E.E_SHAPE

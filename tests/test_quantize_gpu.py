@@ -90,3 +90,44 @@ def test_quantised_activations_feed_the_dual_gemm(pkg, oracle):
     cpu = [t.cpu() if t is not None else None for t in data]
     fp32 = oracle.dual_gemm_fp32(want_q.view(m, k // 2, 1), cpu[1], cpu[2], want_sf.view(m, k // 16, 1), cpu[4], cpu[5])
     assert oracle.compare(out, fp32.to(torch.float16), 1e-3, 1e-3, expected_fp32=fp32) == []
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 128, 256), (512, 384, 1024), (2048, 1024, 512)])
+@pytest.mark.parametrize("dist", ["reference", "uniform16"])
+def test_dual_gemm_with_quantised_output_equals_quantising_its_fp16_result(pkg, oracle, m, n, k, dist):
+    data = pkg.inputs.generate_input(m, n, k, 1, 21, dist=dist, device="cuda")
+    a, b1, b2, _, _, _, sfa, sfb1, sfb2, c = data
+    q, sf_perm = pkg.dual_gemm.dual_gemm_quantized(a, b1, b2, sfa, sfb1, sfb2)
+    c.fill_(float("nan"))
+    plain = pkg.dual_gemm.custom_kernel(data, variant=5)      # same kernel, fp16 output
+    torch.cuda.synchronize()
+    assert pkg._lib.read_status(0) == 0
+    want_q, want_sf = oracle.quantize_nvfp4(plain[:, :, 0].cpu())
+    assert torch.equal(q.view(torch.uint8).cpu()[:, :, 0], want_q)
+    assert torch.equal(_unpermute(oracle, sf_perm, m, n), want_sf)
+    assert pkg.formats.is_kernel_sf_layout(sf_perm, m, n, 1)
+
+
+def test_quantised_output_feeds_a_second_gemm(pkg, oracle):
+    # SwiGLU FFN: h = silu(x W1^T) * (x W2^T) quantised in the epilogue, then y = h W3^T as a one-group GEMM
+    m, n, k = 256, 512, 256
+    data = pkg.inputs.generate_input(m, n, k, 1, 4, dist="reference", device="cuda")
+    a, b1, b2, _, _, _, sfa, sfb1, sfb2, _c = data
+    hq, hsf = pkg.dual_gemm.dual_gemm_quantized(a, b1, b2, sfa, sfb1, sfb2)
+    down = pkg.inputs.generate_grouped_input([m], [256], [n], 1, 8, dist="reference", device="cuda")
+    (_a3, w3, y), (_sfa3, sfw3), (_sfa3p, sfw3p) = down[0][0], down[1][0], down[2][0]
+    down[0][0] = (hq, w3, y)
+    down[2][0] = (hsf, sfw3p)
+    out = pkg.group_gemm.custom_kernel(down)[0]
+    torch.cuda.synchronize()
+    h_bytes = hq.view(torch.uint8).cpu()
+    h_sf = oracle.unpermute_sf(hsf.cpu(), m, n // 16)
+    want = oracle.gemm_fp32(h_bytes, h_sf, w3.cpu(), sfw3.cpu()).to(torch.float16)
+    assert oracle.compare(out, want, 1e-3, 1e-3) == []
+
+
+def test_quantised_output_needs_m_multiple_of_256(pkg):
+    data = pkg.inputs.generate_input(128, 128, 256, 1, 0, device="cuda")
+    a, b1, b2, _, _, _, sfa, sfb1, sfb2, _c = data
+    with pytest.raises(ValueError, match="256"):
+        pkg.dual_gemm.dual_gemm_quantized(a, b1, b2, sfa, sfb1, sfb2)
