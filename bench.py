@@ -219,6 +219,20 @@ def run_grouped_only(args):
                       "note": "grouped-only run for profiler captures"}), flush=True)
 
 
+def run_quantize_only(args):
+    """`--quantize ROWS,K`: warm-up + timed launches of the fp16 -> NVFP4 quantiser and nothing else."""
+    import torch
+    pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
+    torch.cuda.set_device(0)
+    rows, k = (int(v) for v in args.quantize.split(","))
+    x = torch.randn(rows, k, device="cuda:0", dtype=torch.float16)
+    sec, _, _ = time_launches(torch, lambda i: pkg.quantize.quantize_nvfp4(x), args.steps, args.warmup, lambda: None)
+    nbytes = rows * k * 2 + rows * k // 2 + rows * k // 16
+    print(json.dumps({"workload": f"quantize_f16_m{rows}_k{k}", "us_per_launch": sec / args.steps * 1e6,
+                      "hbm_gbs": nbytes * args.steps / sec / 1e9, "steps": args.steps, "warmup": args.warmup,
+                      "note": "quantiser-only run for profiler captures"}), flush=True)
+
+
 def run_extra(torch, pkg, device, peaks, steps, warmup):
     """Other benchmark configurations, one GPU: microseconds per launch."""
     extra = {}
@@ -474,6 +488,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-timed launches (no e2e, CPU baseline or extras): for profiler captures")
     ap.add_argument("--shape", default=None, help="M,N,K override of the dual-GEMM shape (profiler captures)")
+    ap.add_argument("--quantize", default=None, help="ROWS,K: launch only the activation quantiser (profiler captures)")
     ap.add_argument("--grouped", default=None, choices=["g8", "moe"],
                     help="launch only the G=8 or the 64-expert grouped GEMM (profiler captures, one GPU)")
     args = ap.parse_args()
@@ -486,6 +501,8 @@ def main():
         run_reference(args)
     elif args.grouped:
         run_grouped_only(args)
+    elif args.quantize:
+        run_quantize_only(args)
     else:
         run_ours(args)
 
