@@ -110,19 +110,27 @@ __global__ void __launch_bounds__(256) nvfp4_quantize(const uint16_t* __restrict
     const int chunks_per_row = (blocks_per_row + 31) / 32;   // 512-k stretches
     const int rows_padded = (rows + 127) / 128 * 128;
     const int rest_k = k / 64;
-    const long long total = static_cast<long long>(rows_padded) * chunks_per_row;
-    const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-    for (long long first = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); first < total;
-         first += warps * kUnroll) {
+    // (row, stretch) of a warp's work items advance by a fixed step: one division at entry
+    // instead of one per item
+    const int warps = static_cast<int>(gridDim.x * (blockDim.x >> 5));
+    const int first = static_cast<int>(blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5));
+    const int step_row = warps / chunks_per_row, step_c = warps % chunks_per_row;
+    int cur_row = first / chunks_per_row, cur_c = first % chunks_per_row;
+    while (cur_row < rows_padded) {
         uint4 a[kUnroll], b[kUnroll];
         int row[kUnroll], kb[kUnroll];
         bool live[kUnroll], real[kUnroll];
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
-            const long long chunk = first + u * warps;
-            row[u] = static_cast<int>(chunk / chunks_per_row);
-            kb[u] = static_cast<int>(chunk % chunks_per_row) * 32 + lane;   // 16-k block of this lane
-            live[u] = chunk < total && kb[u] < blocks_per_row;
+            row[u] = cur_row;
+            kb[u] = cur_c * 32 + lane;   // 16-k block of this lane
+            cur_row += step_row;
+            cur_c += step_c;
+            if (cur_c >= chunks_per_row) {
+                cur_c -= chunks_per_row;
+                ++cur_row;
+            }
+            live[u] = row[u] < rows_padded && kb[u] < blocks_per_row;
             real[u] = live[u] && row[u] < rows;
             if (real[u]) {
                 const uint16_t* src = x + static_cast<long long>(row[u]) * ldx + kb[u] * 16;
