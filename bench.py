@@ -418,6 +418,25 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = flops_total * e2e_steps / float(t.item()) / 1e12
 
+    gather_ms = None
+    if args.gather and dist is not None:
+        # optional: full C on every rank (one NCCL all-gather of the column shards), outside the metric
+        shard_c = bufs[0]["c"].permute(1, 2, 0)
+        for _ in range(2):
+            pkg.shard.gather_dual_output(shard_c, N)
+        torch.cuda.synchronize()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(5):
+            full_c = pkg.shard.gather_dual_output(shard_c, N)
+        g1.record()
+        torch.cuda.synchronize()
+        tg = torch.tensor([g0.elapsed_time(g1) / 5], dtype=torch.float64, device=device)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        gather_ms = float(tg.item())
+        assert tuple(full_c.shape) == (M, N, 1)
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -456,6 +475,8 @@ def run_ours(args):
                 "steps": e2e_steps, "overlap": "copy-in, kernel and copy-out of consecutive steps on three streams"},
         "clocks": clocks, "roofline": roofline,
     }
+    if gather_ms is not None:
+        line["c_all_gather_ms"] = gather_ms
     if world == 1:
         cpu_tflops, cpu_dt, threads = cpu_reference_sample(4, 1)
         m_, n_, k_ = CPU_SAMPLE
@@ -488,6 +509,8 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-timed launches (no e2e, CPU baseline or extras): for profiler captures")
     ap.add_argument("--shape", default=None, help="M,N,K override of the dual-GEMM shape (profiler captures)")
+    ap.add_argument("--gather", action="store_true",
+                    help="N > 1: also time one all-gather of the C shards after the timed region and report it")
     ap.add_argument("--quantize", default=None, help="ROWS,K: launch only the activation quantiser (profiler captures)")
     ap.add_argument("--grouped", default=None, choices=["g8", "moe"],
                     help="launch only the G=8 or the 64-expert grouped GEMM (profiler captures, one GPU)")

@@ -58,3 +58,19 @@ def shard_grouped_input(data, rank: int, world: int, balance: bool = False):
     abc, sfs, sfs_perm, sizes = data
     mine = assign_groups(sizes, world, balance)[rank]
     return ([abc[i] for i in mine], [sfs[i] for i in mine], [sfs_perm[i] for i in mine], [sizes[i] for i in mine])
+
+
+def gather_dual_output(c_local, n: int, group=None):
+    """Optional step after a column-sharded dual GEMM: every rank ends up with the full
+    ``C [M, n, L]``.  ``c_local`` is this rank's ``[M, n_local, L]`` shard (any strides).
+    One ``all_gather`` over the process group (NCCL over NVLink on GPUs, gloo on CPU); the
+    data path of the GEMM itself has no collective, so call this only when a consumer
+    needs the whole matrix everywhere.  The reference is single-GPU and has no counterpart."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    m, _, l = c_local.shape
+    parts = [torch.empty((m, hi - lo, l), dtype=c_local.dtype, device=c_local.device)
+             for lo, hi in (column_range(n, r, world) for r in range(world))]
+    dist.all_gather(parts, c_local.contiguous(), group=group)
+    return torch.cat(parts, dim=1)

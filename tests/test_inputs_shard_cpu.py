@@ -113,10 +113,7 @@ d = pkg.inputs.generate_input(128, 768, 256, 1, 9, device="cpu")
 s = pkg.shard.shard_dual_input(d, rank, world)
 mine = orc.dual_gemm_from_permuted(s).contiguous()
 lo, hi = pkg.shard.column_range(768, rank, world)
-widths = [pkg.shard.column_range(768, r, world) for r in range(world)]
-parts = [torch.empty((128, b - a, 1), dtype=torch.float16) for a, b in widths]
-dist.all_gather(parts, mine)          # test-only gather; the data path itself has no collective
-full = torch.cat(parts, dim=1)
+full = pkg.shard.gather_dual_output(mine, 768)   # optional gather; the data path itself has no collective
 assert torch.equal(full.view(torch.int16), orc.dual_gemm(d).view(torch.int16)), "dual shards do not reassemble"
 # grouped GEMM: groups are owned by ranks
 g = pkg.inputs.generate_grouped_input([40, 0, 136, 64, 8], [128, 256, 128, 384, 128], [256] * 5, 5, 2, device="cpu")
