@@ -131,3 +131,22 @@ def test_quantised_output_needs_m_multiple_of_256(pkg):
     a, b1, b2, _, _, _, sfa, sfb1, sfb2, _c = data
     with pytest.raises(ValueError, match="256"):
         pkg.dual_gemm.dual_gemm_quantized(a, b1, b2, sfa, sfb1, sfb2)
+
+
+def test_benchmark_size_fused_output_equals_the_quantiser(pkg, oracle):
+    # M=8192, N=14336, K=4096: 48 tiles per CTA pair, both accumulator buffers in rotation.  The fused epilogue
+    # and the stand-alone quantiser applied to the plain kernel's C must give the same bytes everywhere; a window
+    # of both is checked against the oracle.
+    m, n, k = 8192, 14336, 4096
+    d = pkg.inputs.generate_input(m, n, k, 1, 0, dist="reference", device="cuda")
+    a, b1, b2, _, _, _, sfa, sfb1, sfb2, _c = d
+    q, sf_perm = pkg.dual_gemm.dual_gemm_quantized(a, b1, b2, sfa, sfb1, sfb2)
+    plain = pkg.dual_gemm.custom_kernel(d)
+    q2, sf_perm2 = pkg.quantize.quantize_nvfp4(plain[:, :, 0])
+    torch.cuda.synchronize()
+    assert pkg._lib.read_status(0) == 0
+    assert torch.equal(q.view(torch.uint8), q2.view(torch.uint8))
+    assert torch.equal(sf_perm.view(torch.uint8), sf_perm2.view(torch.uint8))
+    want_q, want_sf = oracle.quantize_nvfp4(plain[:512, :, 0].cpu())
+    assert torch.equal(q.view(torch.uint8).cpu()[:512, :, 0], want_q)
+    assert torch.equal(_unpermute(oracle, sf_perm, m, n)[:512], want_sf)
