@@ -418,6 +418,25 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = flops_total * e2e_steps / float(t.item()) / 1e12
 
+    # MoE grouped GEMM sharded by group (N > 1): every rank generates only the experts it owns
+    # (same seeds as the one-GPU list), no collective on the data path; time = max over ranks
+    moe_sharded = None
+    if dist is not None and not args.no_extra:
+        counts = pkg.inputs.moe_expert_counts(8192, 64, 8, seed=0)
+        sizes = [(c_, 2048, 7168, 1) for c_ in counts]
+        mine = pkg.shard.assign_groups(sizes, world)[rank]
+        gdata = pkg.inputs.generate_grouped_input([counts[i] for i in mine], [2048] * len(mine), [7168] * len(mine),
+                                                  len(mine), 1000 + rank, dist="uniform16", device=device)
+        gsteps = max(5, min(args.steps, 50))
+        gsec, _, _ = time_launches(torch, lambda i: pkg.group_gemm.custom_kernel(gdata), gsteps, 3, barrier)
+        tg = torch.tensor([gsec], dtype=torch.float64, device=device)
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        us = float(tg.item()) / gsteps * 1e6
+        total_flops = sum(2.0 * c_ * 2048 * 7168 for c_ in counts)
+        moe_sharded = {"us_per_launch": us, "tflops": total_flops / us / 1e6, "groups_per_gpu": len(mine),
+                       "parallelism": f"64 experts sharded by group x{world}, no collective"}
+        del gdata
+
     gather_ms = None
     if args.gather and dist is not None:
         # optional: full C on every rank (one NCCL all-gather of the column shards), outside the metric
@@ -477,6 +496,8 @@ def run_ours(args):
     }
     if gather_ms is not None:
         line["c_all_gather_ms"] = gather_ms
+    if moe_sharded is not None:
+        line["extra"] = {"grouped_moe_g64_n2048_k7168_sharded": moe_sharded}
     if world == 1:
         cpu_tflops, cpu_dt, threads = cpu_reference_sample(4, 1)
         m_, n_, k_ = CPU_SAMPLE
