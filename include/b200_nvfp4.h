@@ -29,6 +29,8 @@ extern "C" {
 #define B200_E_VARIANT (-5)   /* unknown kernel variant                          */
 #define B200_E_DRIVER (-6)    /* CUDA driver entry point unavailable             */
 #define B200_E_LIMIT (-7)     /* size beyond a documented maximum                */
+#define B200_E_CAPTURE (-8)   /* the stream is being captured and the call must copy
+                                 from host memory that dies when it returns      */
 
 /* Kernel variants (the `variant` argument of the *_ex entry points). */
 #define B200_VARIANT_AUTO 0       /* library picks by shape: PAIR for dual GEMMs with
@@ -43,13 +45,12 @@ extern "C" {
                                      needs m % 256 == 0.  Grouped GEMM: 256 x 256 tiles,
                                      needs every n % 256 == 0, any m                    */
 
-/* Dual GEMM only: variant = B200_VARIANT_PROBE_BASE + bits runs the persistent
- * kernel with parts of its data path switched off (bit 1: scale-factor stores,
- * 2: three of four MMAs, 3: second B tile, 4: global stores, 5: all loads,
- * 6: scale-factor warps, 7: epilogue warps).  For timing experiments; the output
- * is undefined.  With a workspace of at least 64 KiB, CTA 0 logs clock64 events
- * of its roles there. */
-#define B200_VARIANT_PROBE_BASE 100
+#define B200_VARIANT_SELFTEST_LOST_LOAD 8 /* dual GEMM only, failure-detection self-test: the
+                                     one-CTA kernel with its producer dropping the loads of
+                                     every tile's second k-tile and every on-device wait
+                                     limited to about a millisecond.  The waits give up, the
+                                     launch ends by itself, C is not written and the status
+                                     word becomes non-zero (needs k >= 512)               */
 
 /* Library version string, e.g. "b200nvfp4 0.1 (sm_100a)". */
 const char* b200_version(void);
@@ -133,14 +134,28 @@ int b200_grouped_gemm_nvfp4(int groups, const void* const* a, const void* const*
                             const int* mnk, void* workspace, size_t workspace_bytes, void* stream,
                             int device, uint32_t* status);
 
-/* Same with an explicit kernel variant (AUTO, PERSISTENT or SERIAL) and
- * N-tile width (0 = auto, 128 or 256). */
+/* Same with an explicit kernel variant (AUTO, PERSISTENT, SERIAL or PAIR) and
+ * N-tile width (0 = auto, 128 or 256).
+ *
+ * Both grouped entry points copy the descriptor table from host memory that
+ * dies when the call returns, so a call that has to upload (first use of a
+ * workspace, or changed arguments) is refused with B200_E_CAPTURE while `stream`
+ * is being captured; a repeated call whose table is already in the workspace
+ * only launches.  A repeated call on another stream than the one that uploaded
+ * is ordered behind that upload with an event. */
 int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* const* b,
                                const void* const* sfa, const void* const* sfb, void* const* c,
                                const int* mnk, void* workspace, size_t workspace_bytes, int variant,
                                int tile_n, void* stream, int device, uint32_t* status);
 
 size_t b200_grouped_workspace_bytes(int groups);
+
+/* Tell the library that `workspace` on `device` no longer holds the descriptor
+ * table it last uploaded there (the memory was freed, reused or overwritten), so
+ * the next call uploads again.  workspace == NULL forgets every workspace of the
+ * device.  Call it before releasing a workspace.  The reference rewrites its
+ * pointer tables on every call instead (group_gemm/group_gemm_cute5_v2.py:4319-4345). */
+int b200_grouped_workspace_forget(int device, const void* workspace);
 
 /*
  * Grouped GEMM for callers that have no device memory to give and may not
@@ -153,13 +168,17 @@ size_t b200_grouped_workspace_bytes(int groups);
  * the library's device image instead: B200_STATIC_MAX_GROUPS entries of 384
  * bytes (24 KiB), present on every GPU that loads the library until the process
  * exits.  Arguments and results are those of b200_grouped_gemm_nvfp4 without the
- * workspace; the same kernels run.
+ * workspace.  It always runs the one-CTA-per-tile kernels (128 x 128 or 128 x 256
+ * tiles); the workspace entry point additionally picks the CTA-pair kernel for
+ * large lists.  Both give the same bits.
  *
  *  - groups > B200_STATIC_MAX_GROUPS is rejected with B200_E_LIMIT.
  *  - The call allocates and frees nothing, on the device or through any library.
  *  - The first call on a device looks up the array's device address and does the
  *    library's one-time per-device set-up; make that call before any stream
  *    capture begins.
+ *  - Every call copies the table from the host stack into the array, so a call on
+ *    a stream that is being captured is refused with B200_E_CAPTURE.
  *  - Every call rewrites the entries it uses and all calls share the one array:
  *    two calls whose GPU work can overlap (different streams, or the same stream
  *    from different threads without ordering) race on it.  Calls on one stream
@@ -206,6 +225,14 @@ int b200_quantize_nvfp4(const void* x, int dtype, int rows, int k, int64_t ldx, 
 /* Synchronise `stream`, copy the library-owned status word of `device` into
  * *out and clear it. */
 int b200_read_status(int device, void* stream, uint32_t* out);
+
+/* Synchronise `stream` and return the SM-clock cycles (clock64) that the first
+ * CTA of the last GEMM launch on `device` spent from entry to exit.  Divided by
+ * the launch's CUDA-event time this gives the SM clock the launch really ran at,
+ * which nvidia-smi cannot sample inside a millisecond-long region.  The
+ * reference gathers the same kind of figure with in-kernel clock64 probes
+ * (group_gemm/group_gemm_cute4.py:67-79, 622-637). */
+int b200_read_last_cycles(int device, void* stream, uint64_t* out);
 
 /* Number of kernels this library has launched in the calling process. */
 uint64_t b200_launch_count(void);

@@ -14,7 +14,9 @@ LIB_PATH = os.path.join(HERE, "libb200nvfp4.so")
 
 VARIANT_AUTO, VARIANT_PERSISTENT, VARIANT_SERIAL, VARIANT_SERIAL_2MMA, VARIANT_SPLITK, VARIANT_PAIR = 0, 1, 2, 3, 4, 5
 
-E_NULL, E_SHAPE, E_ALIGN, E_WORKSPACE, E_VARIANT, E_DRIVER, E_LIMIT = -1, -2, -3, -4, -5, -6, -7
+VARIANT_SELFTEST_LOST_LOAD = 8
+
+E_NULL, E_SHAPE, E_ALIGN, E_WORKSPACE, E_VARIANT, E_DRIVER, E_LIMIT, E_CAPTURE = -1, -2, -3, -4, -5, -6, -7, -8
 
 STATIC_MAX_GROUPS = 64
 DTYPE_F16, DTYPE_BF16 = 0, 1
@@ -40,6 +42,8 @@ SIGNATURES = {
     "b200_quantize_sf_bytes": (_sz, [_i, _i]),
     "b200_quantize_nvfp4": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp, _i]),
     "b200_read_status": (_i, [_i, _vp, _u32p]),
+    "b200_read_last_cycles": (_i, [_i, _vp, ctypes.POINTER(ctypes.c_uint64)]),
+    "b200_grouped_workspace_forget": (_i, [_i, _vp]),
 }
 
 _lib = None
@@ -86,6 +90,21 @@ def read_status(device: int, stream: int = 0) -> int:
     out = ctypes.c_uint32(0)
     check(load().b200_read_status(device, stream, ctypes.byref(out)))
     return out.value
+
+
+def raise_on_status(device: int, stream: int = 0) -> None:
+    """Synchronise and raise B200Error if a bounded on-device wait gave up since the last check."""
+    word = read_status(device, stream)
+    if word:
+        raise B200Error(word, f"device status word {word:#x}: an on-device wait ran out (bits: 1 producer, 2/4 MMA, "
+                              f"8 epilogue, 0x10 serial, 0x20 split-k, 0x40 scale factors, 0x80 CTA pair)")
+
+
+def last_launch_cycles(device: int, stream: int = 0) -> int:
+    """SM-clock cycles the first CTA of the last GEMM launch on ``device`` ran for."""
+    out = ctypes.c_uint64(0)
+    check(load().b200_read_last_cycles(device, stream, ctypes.byref(out)))
+    return int(out.value)
 
 
 def launch_count() -> int:

@@ -23,6 +23,7 @@ uint64_t g_launches = 0;
 uint64_t g_epoch = 0;                  // split-k launches so far (their flag value)
 
 __device__ uint32_t g_device_status;   // library-owned status word (one per device)
+__device__ unsigned long long g_device_cycles;   // clock64 span of CTA 0 of the last GEMM launch (one per device)
 
 int fail(int code, const char* fmt, ...) {
     char buf[512];
@@ -108,6 +109,7 @@ struct DeviceState {
     bool ready = false;
     int sm_count = 0;
     uint32_t* status = nullptr;
+    unsigned long long* cycles = nullptr;
 };
 std::map<int, DeviceState> g_devices;
 
@@ -116,6 +118,7 @@ template <typename K> int opt_in_smem(K kernel, uint32_t bytes) {
     return 0;
 }
 
+constexpr int B200_VARIANT_LAST = B200_VARIANT_SELFTEST_LOST_LOAD;
 constexpr int kDualStages = 4;
 constexpr int kG128Stages = 6;
 constexpr int kG256Stages = 4;
@@ -135,9 +138,16 @@ int device_state(int device, DeviceState** out) {
         B200_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device));
         B200_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&st.status), g_device_status));
         B200_CUDA(cudaMemset(st.status, 0, sizeof(uint32_t)));
+        B200_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&st.cycles), g_device_cycles));
+        B200_CUDA(cudaMemset(st.cycles, 0, sizeof(unsigned long long)));
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Dual, kDualStages>,
                               smem_bytes_persistent<Mode::Dual, kDualStages>()))) return rc;
+#ifdef B200_TIMING_PROBES
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Dual, kDualStages, true>,
+                              smem_bytes_persistent<Mode::Dual, kDualStages>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDual, true>, kPairSmemBytes))) return rc;
+#endif
+        if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Dual, kDualStages, false, true>,
                               smem_bytes_persistent<Mode::Dual, kDualStages>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Group128, kG128Stages>,
                               smem_bytes_persistent<Mode::Group128, kG128Stages>()))) return rc;
@@ -178,9 +188,11 @@ struct DualKey {
     const void *a, *b1, *b2, *c;
     int m, n, k, l, device;
     long long b_batch, ldc, c_batch;
+    bool quant;   // quantised-output call: `c` is the packed output and the entry holds no fp16 store map
     bool operator==(const DualKey& o) const {
         return a == o.a && b1 == o.b1 && b2 == o.b2 && c == o.c && m == o.m && n == o.n && k == o.k && l == o.l &&
-               device == o.device && b_batch == o.b_batch && ldc == o.ldc && c_batch == o.c_batch;
+               device == o.device && b_batch == o.b_batch && ldc == o.ldc && c_batch == o.c_batch &&
+               quant == o.quant;
     }
 };
 struct DualMaps {
@@ -225,10 +237,10 @@ size_t splitk_bytes(size_t tiles, int splits) {
     return splits <= 1 ? 0 : splitk_flag_bytes(tiles) + tiles * splits * 128 * 256 * sizeof(float);
 }
 
-template <Mode M, int kStages, typename P, bool kTimingProbes = false>
+template <Mode M, int kStages, typename P, bool kTimingProbes = false, bool kInjectLostLoad = false>
 int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStream_t stream) {
     const int grid = units < sm_count ? units : sm_count;
-    nvfp4_gemm_persistent<M, kStages, kTimingProbes>
+    nvfp4_gemm_persistent<M, kStages, kTimingProbes, kInjectLostLoad>
         <<<grid, kPersistentThreads, smem_bytes_persistent<M, kStages>(), stream>>>(prob, flags);
     B200_CUDA(cudaGetLastError());
     ++g_launches;
@@ -236,8 +248,8 @@ int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStr
 }
 
 // CTA pairs: clusters of two CTAs, one pair per TPC, each pair walks pair tiles.
-template <typename S> int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, int flags,
-                                      cudaStream_t stream) {
+template <typename S, bool kTimingProbes = false>
+int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, int flags, cudaStream_t stream) {
     int pairs = sm_count / 2;
     if (pairs > pair_tiles) pairs = pair_tiles;
     cudaLaunchConfig_t cfg;
@@ -253,7 +265,7 @@ template <typename S> int launch_pair(const typename S::Params& prob, int pair_t
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    B200_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair<S>, prob, flags));
+    B200_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair<S, kTimingProbes>, prob, flags));
     ++g_launches;
     return 0;
 }
@@ -299,9 +311,18 @@ static int dual_gemm_impl(const void* a, const void* b1, const void* b2, const v
     if (sfb_batch_bytes == 0) sfb_batch_bytes = static_cast<int64_t>(n / 128) * (k / 64) * 512;
     int rc = validate_dual(a, b1, b2, sfa, sfb1, sfb2, c, m, n, k, l, ldc, c_batch, b_batch_bytes, sfb_batch_bytes);
     if (rc) return rc;
-    const bool probe = variant >= B200_VARIANT_PROBE_BASE && variant < B200_VARIANT_PROBE_BASE + 256;
-    const bool pair_probe = variant >= B200_VARIANT_PROBE_BASE + 300 && variant < B200_VARIANT_PROBE_BASE + 556;
-    if (!probe && !pair_probe && (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_PAIR))
+#ifdef B200_TIMING_PROBES
+    // Instrumented build only: variant = kProbeBase + bits runs the one-CTA kernel, kProbeBase + 300 + bits
+    // the CTA-pair kernel, with parts of the data path switched off (kFlag* bits; the output is then wrong by
+    // design) and, given a 64 KiB workspace, a clock64 event log of CTA 0.
+    constexpr int kProbeBase = 100;
+    const bool probe = variant >= kProbeBase && variant < kProbeBase + 256;
+    const bool pair_probe = variant >= kProbeBase + 300 && variant < kProbeBase + 556;
+#else
+    constexpr int kProbeBase = 0;
+    constexpr bool probe = false, pair_probe = false;
+#endif
+    if (!probe && !pair_probe && (variant < B200_VARIANT_AUTO || variant > B200_VARIANT_LAST))
         return fail(B200_E_VARIANT, "dual gemm: unknown variant %d", variant);
 
     std::lock_guard<std::mutex> lock(g_mutex);
@@ -312,7 +333,7 @@ static int dual_gemm_impl(const void* a, const void* b1, const void* b2, const v
 
     DenseProblem p;
     memset(&p, 0, sizeof p);
-    DualKey key{a, b1, b2, c, m, n, k, l, device, b_batch_bytes, ldc, c_batch};
+    DualKey key{a, b1, b2, c, m, n, k, l, device, b_batch_bytes, ldc, c_batch, quant};
     const DualMaps* maps = nullptr;
     for (const DualMaps& e : g_dual_cache)
         if (e.key == key) { maps = &e; break; }
@@ -350,15 +371,21 @@ static int dual_gemm_impl(const void* a, const void* b1, const void* b2, const v
     p.sf_k_atoms = k / 64;
     p.k_splits = 1;
     p.status = status ? status : st->status;
+    p.cycles = st->cycles;
     // timing probes: an optional 8 x 1024 x 8-byte event log for CTA 0
     p.trace = ((probe || pair_probe) && workspace && workspace_bytes >= 8 * 1024 * sizeof(unsigned long long))
                   ? static_cast<unsigned long long*>(workspace) : nullptr;
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (quant) return launch_pair<PairDualQuant>(p, dual_pair_tiles(p), st->sm_count, 0, s);
+#ifdef B200_TIMING_PROBES
     if (probe)
         return launch_persistent<Mode::Dual, kDualStages, DenseProblem, true>(p, p.total_tiles, st->sm_count,
-                                                                              variant - B200_VARIANT_PROBE_BASE, s);
+                                                                              variant - kProbeBase, s);
+    if (pair_probe && p.m_tiles % 2 == 0)
+        return launch_pair<PairDual, true>(p, dual_pair_tiles(p), st->sm_count, variant - kProbeBase - 300, s);
+#endif
+    (void)kProbeBase;
     // Split-k only on request (B200_VARIANT_SPLITK): its partial-sum exchange through
     // global memory currently costs more than the idle SMs it puts to work.
     if (variant == B200_VARIANT_SPLITK) {
@@ -377,8 +404,6 @@ static int dual_gemm_impl(const void* a, const void* b1, const void* b2, const v
     }
     if (p.k_splits > 1)
         return launch_persistent<Mode::Dual, kDualStages>(p, p.total_tiles * p.k_splits, st->sm_count, 0, s);
-    if (pair_probe && p.m_tiles % 2 == 0)
-        return launch_pair<PairDual>(p, dual_pair_tiles(p), st->sm_count, variant - B200_VARIANT_PROBE_BASE - 300, s);
     if (variant == B200_VARIANT_PAIR) {
         if (p.m_tiles % 2) return fail(B200_E_SHAPE, "dual gemm: CTA pairs need m to be a multiple of 256 (m=%d)", m);
         return launch_pair<PairDual>(p, dual_pair_tiles(p), st->sm_count, 0, s);
@@ -392,6 +417,11 @@ static int dual_gemm_impl(const void* a, const void* b1, const void* b2, const v
             return launch_serial<Mode::Dual>(p, p.total_tiles, 0, s);
         case B200_VARIANT_SERIAL_2MMA:
             return launch_serial<Mode::Dual>(p, p.total_tiles, 1, s);
+        case B200_VARIANT_SELFTEST_LOST_LOAD:
+            // failure-detection self-test: the producer drops one k-tile's loads, the waits give up
+            // after about a millisecond, the status word becomes non-zero and C stays unwritten
+            return launch_persistent<Mode::Dual, kDualStages, DenseProblem, false, true>(p, p.total_tiles,
+                                                                                         st->sm_count, 0, s);
         default:
             return launch_persistent<Mode::Dual, kDualStages>(p, p.total_tiles, st->sm_count, 0, s);
     }
@@ -434,14 +464,73 @@ size_t b200_grouped_workspace_bytes(int groups) {
 
 namespace b200 {
 namespace {
+constexpr int kTilingPair = -256;   // `tiling` value that selects 256 x 256 CTA-pair tiles
+
+// Fills `table[0 .. groups)` for the given tiling (128 or 256 output columns per one-CTA
+// tile, or kTilingPair) and returns the number of tiles through *total_tiles.
+int build_group_table(GroupEntry* table, int groups, const void* const* a, const void* const* b,
+                      const void* const* sfa, const void* const* sfb, void* const* c, const int* mnk, int tiling,
+                      int* total_tiles) {
+    memset(table, 0, static_cast<size_t>(groups) * sizeof(GroupEntry));
+    const bool pair = tiling == kTilingPair;
+    int tile_begin = 0, rc;
+    for (int g = 0; g < groups; ++g) {
+        const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
+        GroupEntry& e = table[g];
+        e.m = m;
+        e.n = n;
+        e.k_tiles = k / 256;
+        e.m_tiles = pair ? (m + 255) / 256 : (m + 127) / 128;
+        e.n_tiles = pair ? n / 256 : (n + tiling - 1) / tiling;
+        e.tile_begin = tile_begin;
+        e.sf_k_atoms = k / 64;
+        e.sfb_row_atoms = n / 128;
+        e.ldc = n;
+        tile_begin += e.m_tiles * e.n_tiles;
+        if (m == 0) continue;
+        e.sfa = static_cast<const uint8_t*>(sfa[g]);
+        e.sfb = static_cast<const uint8_t*>(sfb[g]);
+        e.c = static_cast<__half*>(c[g]);
+        if ((rc = encode_operand_map(&e.map_a, a[g], m, k, 1, static_cast<long long>(m) * (k / 2)))) return rc;
+        if ((rc = encode_operand_map(&e.map_b, b[g], n, k, 1, static_cast<long long>(n) * (k / 2)))) return rc;
+    }
+    *total_tiles = tile_begin;
+    return 0;
+}
+
 // What the library last wrote to a given workspace address, so identical
-// descriptor tables are not rebuilt or re-uploaded on every call.
+// descriptor tables are not rebuilt or re-uploaded on every call.  An entry is
+// only as good as the caller's promise not to touch the workspace in between:
+// b200_grouped_workspace_forget() withdraws it (the Python wrapper calls that
+// whenever a workspace changes hands).
 struct WorkspaceImage {
     std::vector<uint8_t> key;       // raw call arguments
     int total_tiles = 0;
     int tile_n = 0;
+    cudaStream_t upload_stream = nullptr;   // stream the table was copied on ...
+    cudaEvent_t uploaded = nullptr;         // ... and the event recorded behind that copy
 };
 std::map<std::pair<int, const void*>, WorkspaceImage> g_workspaces;
+
+void drop_workspace_images() {
+    for (auto& kv : g_workspaces)
+        if (kv.second.uploaded) cudaEventDestroy(kv.second.uploaded);
+    g_workspaces.clear();
+}
+
+// The table copy of a grouped call has a host stack / heap source that dies when the
+// call returns: under stream capture it would become a graph node that re-reads dead
+// memory on every replay.  Such calls are refused.
+int reject_capture(cudaStream_t s, const char* what) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaError_t e = cudaStreamIsCapturing(s, &cs);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamIsCapturing");
+    if (cs != cudaStreamCaptureStatusNone)
+        return fail(B200_E_CAPTURE,
+                    "%s: the stream is being captured and this call has to upload its descriptor table; "
+                    "make the call once outside the capture first", what);
+    return 0;
+}
 }  // namespace
 }  // namespace b200
 
@@ -500,7 +589,7 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     // each pair of SMs gets at least two tiles
     const bool use_pair = variant == B200_VARIANT_PAIR ||
                           (variant == B200_VARIANT_AUTO && tile_n_chosen_here && all_n256 && pair_tiles >= st->sm_count);
-    if (use_pair) tile_n = -256;   // marks the pair tiling in the cache key and the table
+    if (use_pair) tile_n = kTilingPair;   // marks the pair tiling in the cache key and the table
 
     std::vector<uint8_t> key(sizeof(int) * 2 + groups * (5 * sizeof(void*) + 3 * sizeof(int)));
     {
@@ -515,43 +604,28 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
         put(c, groups * sizeof(void*));
         put(mnk, groups * 3 * sizeof(int));
     }
+    if (g_workspaces.size() > 256 && !g_workspaces.count({device, workspace})) drop_workspace_images();
     WorkspaceImage& img = g_workspaces[{device, workspace}];
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (img.key != key) {
+        if ((rc = reject_capture(s, "grouped gemm"))) return rc;
         std::vector<GroupEntry> table(groups);
-        memset(table.data(), 0, groups * sizeof(GroupEntry));
-        int tile_begin = 0;
-        for (int g = 0; g < groups; ++g) {
-            const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
-            GroupEntry& e = table[g];
-            e.m = m;
-            e.n = n;
-            e.k_tiles = k / 256;
-            e.m_tiles = use_pair ? (m + 255) / 256 : (m + 127) / 128;
-            e.n_tiles = use_pair ? n / 256 : (n + tile_n - 1) / tile_n;
-            e.tile_begin = tile_begin;
-            e.sf_k_atoms = k / 64;
-            e.sfb_row_atoms = n / 128;
-            e.ldc = n;
-            tile_begin += e.m_tiles * e.n_tiles;
-            if (m == 0) continue;
-            e.sfa = static_cast<const uint8_t*>(sfa[g]);
-            e.sfb = static_cast<const uint8_t*>(sfb[g]);
-            e.c = static_cast<__half*>(c[g]);
-            if ((rc = encode_operand_map(&e.map_a, a[g], m, k, 1, static_cast<long long>(m) * (k / 2)))) return rc;
-            if ((rc = encode_operand_map(&e.map_b, b[g], n, k, 1, static_cast<long long>(n) * (k / 2)))) return rc;
-        }
+        int total = 0;
+        if ((rc = build_group_table(table.data(), groups, a, b, sfa, sfb, c, mnk, tile_n, &total)))
+            return rc;
         // Pageable source: the runtime stages the bytes before returning, so
         // `table` may go out of scope while the copy is still queued.
+        img.key.clear();   // if anything below fails the entry must not look valid
         B200_CUDA(cudaMemcpyAsync(workspace, table.data(), groups * sizeof(GroupEntry), cudaMemcpyHostToDevice, s));
+        if (!img.uploaded) B200_CUDA(cudaEventCreateWithFlags(&img.uploaded, cudaEventDisableTiming));
+        B200_CUDA(cudaEventRecord(img.uploaded, s));
+        img.upload_stream = s;
         img.key = key;
-        img.total_tiles = tile_begin;
+        img.total_tiles = total;
         img.tile_n = tile_n;
-        if (g_workspaces.size() > 256) {   // bound the bookkeeping
-            WorkspaceImage keep = img;
-            g_workspaces.clear();
-            g_workspaces[{device, workspace}] = keep;
-        }
+    } else if (img.upload_stream != s) {
+        // same table, another stream: order this launch behind the copy that wrote it
+        B200_CUDA(cudaStreamWaitEvent(s, img.uploaded, 0));
     }
     const WorkspaceImage& cur = g_workspaces[{device, workspace}];
     GroupedProblem p;
@@ -559,8 +633,9 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     p.num_groups = groups;
     p.total_tiles = cur.total_tiles;
     p.status = status ? status : st->status;
+    p.cycles = st->cycles;
     p.trace = nullptr;
-    if (cur.tile_n == -256) return launch_pair<PairGrouped>(p, p.total_tiles, st->sm_count, 0, s);
+    if (cur.tile_n == kTilingPair) return launch_pair<PairGrouped>(p, p.total_tiles, st->sm_count, 0, s);
     if (variant == B200_VARIANT_SERIAL) {
         return cur.tile_n == 256 ? launch_serial<Mode::Group256>(p, p.total_tiles, 0, s)
                                  : launch_serial<Mode::Group128>(p, p.total_tiles, 0, s);
@@ -575,6 +650,27 @@ int b200_grouped_gemm_nvfp4(int groups, const void* const* a, const void* const*
                             size_t workspace_bytes, void* stream, int device, uint32_t* status) {
     return b200_grouped_gemm_nvfp4_ex(groups, a, b, sfa, sfb, c, mnk, workspace, workspace_bytes, B200_VARIANT_AUTO,
                                       0, stream, device, status);
+}
+
+int b200_grouped_workspace_forget(int device, const void* workspace) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (workspace == nullptr) {           // every workspace of the device
+        for (auto it = g_workspaces.begin(); it != g_workspaces.end();) {
+            if (it->first.first == device) {
+                if (it->second.uploaded) cudaEventDestroy(it->second.uploaded);
+                it = g_workspaces.erase(it);
+            } else {
+                ++it;
+            }
+        }
+        return 0;
+    }
+    auto it = g_workspaces.find({device, workspace});
+    if (it != g_workspaces.end()) {
+        if (it->second.uploaded) cudaEventDestroy(it->second.uploaded);
+        g_workspaces.erase(it);
+    }
+    return 0;
 }
 
 }  // extern "C"
@@ -648,31 +744,12 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
     if ((rc = static_table_address(device, &table_dev))) return rc;
 
     const int tile_n = (all_n256 && tiles128 / 2 >= 2LL * st->sm_count) ? 256 : 128;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if ((rc = reject_capture(s, "grouped gemm (static table)"))) return rc;
     // Host copy of the table on the stack (24 KiB at most): nothing is allocated.
     GroupEntry table[B200_STATIC_MAX_GROUPS];
-    memset(table, 0, static_cast<size_t>(groups) * sizeof(GroupEntry));
     int tile_begin = 0;
-    for (int g = 0; g < groups; ++g) {
-        const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
-        GroupEntry& e = table[g];
-        e.m = m;
-        e.n = n;
-        e.k_tiles = k / 256;
-        e.m_tiles = (m + 127) / 128;
-        e.n_tiles = (n + tile_n - 1) / tile_n;
-        e.tile_begin = tile_begin;
-        e.sf_k_atoms = k / 64;
-        e.sfb_row_atoms = n / 128;
-        e.ldc = n;
-        tile_begin += e.m_tiles * e.n_tiles;
-        if (m == 0) continue;
-        e.sfa = static_cast<const uint8_t*>(sfa[g]);
-        e.sfb = static_cast<const uint8_t*>(sfb[g]);
-        e.c = static_cast<__half*>(c[g]);
-        if ((rc = encode_operand_map(&e.map_a, a[g], m, k, 1, static_cast<long long>(m) * (k / 2)))) return rc;
-        if ((rc = encode_operand_map(&e.map_b, b[g], n, k, 1, static_cast<long long>(n) * (k / 2)))) return rc;
-    }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if ((rc = build_group_table(table, groups, a, b, sfa, sfb, c, mnk, tile_n, &tile_begin))) return rc;
     // Every entry this launch reads is rewritten here, so nothing left by an earlier
     // call is ever consumed; entries beyond `groups` keep stale bytes and are not read.
     // The source is pageable stack memory: the runtime has copied it out by the time
@@ -684,6 +761,7 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
     p.num_groups = groups;
     p.total_tiles = tile_begin;
     p.status = status ? status : st->status;
+    p.cycles = st->cycles;
     p.trace = nullptr;
     return tile_n == 256 ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s)
                          : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s);
@@ -729,6 +807,22 @@ int b200_quantize_nvfp4(const void* x, int dtype, int rows, int k, int64_t ldx, 
     }
     B200_CUDA(cudaGetLastError());
     ++g_launches;
+    return 0;
+}
+
+int b200_read_last_cycles(int device, void* stream, uint64_t* out) {
+    if (!out) return fail(B200_E_NULL, "read_last_cycles: out is NULL");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    int rc;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    B200_CUDA(cudaStreamSynchronize(s));
+    unsigned long long v = 0;
+    B200_CUDA(cudaMemcpy(&v, st->cycles, sizeof v, cudaMemcpyDeviceToHost));
+    *out = v;
     return 0;
 }
 

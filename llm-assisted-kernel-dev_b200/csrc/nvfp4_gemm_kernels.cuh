@@ -110,6 +110,7 @@ struct alignas(64) DenseProblem {
     int sf_k_atoms;                      // k / 64
     int k_splits;                        // 1 unless split-k
     uint32_t* status;
+    unsigned long long* cycles;          // CTA 0 stores its clock64 span here (one store per launch)
 };
 
 // Grouped GEMM: one entry per group in device memory (the workspace).
@@ -131,6 +132,7 @@ struct GroupedProblem {
     int total_tiles;
     uint32_t* status;
     unsigned long long* trace;           // timing probes only
+    unsigned long long* cycles;          // CTA 0 stores its clock64 span here (one store per launch)
 };
 
 // One unit of work: a 128-row output tile.
@@ -630,18 +632,21 @@ constexpr int kSfSets = 1;
 constexpr int kFirstSfWarp = kSfSets == 2 ? 8 : 6;
 constexpr int kPersistentThreads = 32 * (kFirstSfWarp + 4 * kSfSets);
 
-template <Mode M, int kStages, bool kTimingProbes = false>
+template <Mode M, int kStages, bool kTimingProbes = false, bool kInjectLostLoad = false>
 __global__ void __launch_bounds__(kPersistentThreads, 1)
 nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, int flags) {
     using L = StageLayout<M>;
     using TM = TmemMap<M>;
     using S = Scheduler<M>;
+    // fault-injection self-test: the producer drops the loads of one k-tile, every wait gives up early
+    constexpr long long kLimit = kInjectLostLoad ? kShortWaitTimeoutCycles : kWaitTimeoutCycles;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     ControlBlock* ctl = reinterpret_cast<ControlBlock*>(smem_raw + (smem_base - smem_u32(smem_raw)) +
                                                         kStages * L::kBytes);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const long long launch_t0 = clock64();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -716,7 +721,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
         uint32_t v[kKBlocks * kWordsPerBlock];
         bool loaded = false;
         auto load_k_tile = [&](uint32_t stage_index, uint32_t phase) -> bool {
-            if (!mbar_wait<true>(smem_u32(&ctl->full[stage_index]), phase, abort_flag, p.status, kStatusSfWait))
+            if (!mbar_wait<true, kLimit>(smem_u32(&ctl->full[stage_index]), phase, abort_flag, p.status, kStatusSfWait))
                 return false;
             const uint32_t src = smem_base + stage_index * L::kBytes + lane * 16;
 #pragma unroll
@@ -760,7 +765,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                                 if (++rs == kStages) { rs = 0; rph ^= 1u; }
                             }
                             while (ok && retired <= need) {
-                                ok = mbar_wait<true>(smem_u32(&ctl->empty[rs]), rph, abort_flag, p.status, kStatusSfWait);
+                                ok = mbar_wait<true, kLimit>(smem_u32(&ctl->empty[rs]), rph, abort_flag, p.status, kStatusSfWait);
                                 ++retired;
                                 if (++rs == kStages) { rs = 0; rph ^= 1u; }
                             }
@@ -810,12 +815,16 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                     last_group = w.group;
                 }
                 for (int i = 0; i < w.k_tile_count; ++i) {
-                    if (!mbar_wait<true>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
+                    if (!mbar_wait<true, kLimit>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
                                          kStatusProducerWait)) {
                         ok = false;
                         break;
                     }
                     trace(1);   // stage free, loads issued
+                    if (kInjectLostLoad && i == 1) {   // self-test: this k-tile never arrives
+                        if (++s == kStages) { s = 0; ph ^= 1u; }
+                        continue;
+                    }
                     issue_stage_loads<M, kTimingProbes>(w, w.k_tile_begin + i, smem_base + s * L::kBytes,
                                                         smem_u32(&ctl->full[s]), flags);
                     if (++s == kStages) { s = 0; ph ^= 1u; }
@@ -861,7 +870,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                 const Work w = S::get(p, unit, cursor);
                 if (it > 0 && !no_epi) {
                     const int r = it - 1;   // wait for hand-back number r
-                    if (!mbar_wait(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
+                    if (!mbar_wait<false, kLimit>(smem_u32(&ctl->acc_release[r & 1]), (r >> 1) & 1, abort_flag, p.status,
                                    kStatusMmaWaitAcc)) {
                         failed = true;
                         break;
@@ -880,7 +889,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                 for (int i = 0; i < k_tiles; ++i) {
                     if (kIssuers == 1 || (kt % kIssuers) == me) {
                         if (kIssuers > 1 && !first_done) {
-                            if (!mbar_wait(first_empty, first_parity, abort_flag, p.status, kStatusMmaWaitAcc)) {
+                            if (!mbar_wait<false, kLimit>(first_empty, first_parity, abort_flag, p.status, kStatusMmaWaitAcc)) {
                                 failed = true;
                                 break;
                             }
@@ -888,7 +897,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                         }
                         const uint32_t bar = no_sf ? smem_u32(&ctl->full[s]) : sf_ready_bar + (kt & 3u) * 8u;
                         const uint32_t parity = no_sf ? s_use & 1u : (kt >> 2) & 1u;
-                        if (!mbar_wait(bar, parity, abort_flag, p.status, kStatusMmaWaitFull)) {
+                        if (!mbar_wait<false, kLimit>(bar, parity, abort_flag, p.status, kStatusMmaWaitFull)) {
                             failed = true;
                             break;
                         }
@@ -920,7 +929,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
             }
             // drain: every MMA issued above must retire before TMEM is freed
             tc_commit(smem_u32(&ctl->aux[me]));
-            mbar_wait(smem_u32(&ctl->aux[me]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
+            mbar_wait<false, kLimit>(smem_u32(&ctl->aux[me]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
         }
         __syncwarp();
     } else if (warp < 4) {
@@ -936,7 +945,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                 __syncwarp();
                 if (lane == 0) mbar_arrive(release_bar);
             }
-            if (!mbar_wait<true>(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
+            if (!mbar_wait<true, kLimit>(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
                                  kStatusEpilogueWait)) {
                 ok = false;
                 break;
@@ -965,6 +974,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemColumns);
     }
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.cycles) *p.cycles = static_cast<unsigned long long>(clock64() - launch_t0);
 }
 
 // ---------------------------------------------------------------------------

@@ -267,7 +267,7 @@ __device__ __forceinline__ void epilogue_tile_quant(const DenseProblem& p, const
     }
 }
 
-template <typename S>
+template <typename S, bool kTimingProbes = false>
 __global__ void __launch_bounds__(320, 1)
 nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
     using TM = TmemMap<Mode::Dual>;          // same TMEM map for both: 256 accumulator columns per buffer
@@ -284,6 +284,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
     const int pair = blockIdx.x >> 1;
     const int pairs = gridDim.x >> 1;
     const int total = S::total(p);
+    const long long launch_t0 = clock64();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPairStages; ++s) {
@@ -332,7 +333,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 trace(1);   // operands landed
                 uint32_t v[kKBlocks * 12];
                 const uint32_t src = smem_base + s * PairStage::kBytes + lane * 16;
-                if (!(flags & kFlagSkipBHi))   // timing probe (bit reused): no scale-factor reads at all
+                if (!(kTimingProbes && (flags & kFlagSkipBHi)))   // timing probe (bit reused): no scale-factor reads
 #pragma unroll
                 for (int kb = 0; kb < kKBlocks; ++kb) {
                     uint32_t* d = v + kb * 12;
@@ -342,7 +343,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 }
                 // ring units of this k-tile were last read by k-tile (units + 1 - kBuffers) / 2
                 const uint32_t last_unit = units + kUnitsPerKTile - 1;
-                const bool probe_skip = (flags & kFlagSkipSfCopy) && kt >= 2;   // timing probe
+                const bool probe_skip = kTimingProbes && (flags & kFlagSkipSfCopy) && kt >= 2;   // timing probe
                 if (!probe_skip && last_unit >= static_cast<uint32_t>(TM::kBuffers)) {
                     const uint32_t need = (last_unit - TM::kBuffers) / kUnitsPerKTile;
                     if (retired <= need) {
@@ -404,7 +405,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     trace(1);   // stage free
                     const uint32_t stage = smem_base + s * PairStage::kBytes;
                     const uint32_t bar = smem_u32(&ctl->full[s]);
-                    if (flags & kFlagSkipLoads) {   // timing probe
+                    if (kTimingProbes && (flags & kFlagSkipLoads)) {   // timing probe
                         mbar_arrive(bar);
                         if (++s == kPairStages) { s = 0; ph ^= 1u; }
                         continue;
@@ -436,7 +437,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
             uint32_t s = 0, ph = 0, a_lo = desc_lo_base, buf = 0;
             int it = 0;
             bool failed = false;
-            Tracer trace(lane == 0 ? p.trace : nullptr, 0);
+            Tracer trace(kTimingProbes && lane == 0 ? p.trace : nullptr, 0);
             const long long kernel_t0 = clock64();
             int cursor = 0;
             for (int tile = pair; tile < total && !failed; tile += pairs, ++it) {
@@ -493,13 +494,13 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
             }
             tc_commit_pair_elect(smem_u32(&ctl->aux[0]));
             mbar_wait<true>(smem_u32(&ctl->aux[0]), 0, abort_flag, p.status, kStatusMmaWaitAcc);
-            if (lane == 0 && p.trace && blockIdx.x == 0) p.trace[8 * 1024 - 1] = static_cast<unsigned long long>(clock64() - kernel_t0);
+            if (kTimingProbes && lane == 0 && p.trace && blockIdx.x == 0) p.trace[8 * 1024 - 1] = static_cast<unsigned long long>(clock64() - kernel_t0);
         }
         __syncwarp();
     } else if (warp < 4) {
         // ------------------------------ epilogue (each CTA its own 128 rows)
         int it = 0, cursor = 0;
-        Tracer trace(lane == 0 && blockIdx.x == 0 ? p.trace : nullptr, warp == 0 ? 7 : warp);
+        Tracer trace(kTimingProbes && lane == 0 && blockIdx.x == 0 ? p.trace : nullptr, warp == 0 ? 7 : warp);
         for (int tile = pair; tile < total; tile += pairs, ++it) {
             const Work w = S::get(p, tile, rank, cursor);
             const uint32_t release_bar = map_to_cta(smem_u32(&ctl->acc_release[it & 1]), 0);
@@ -508,7 +509,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 break;
             tc_fence_after_sync();
             trace(1);   // accumulator complete
-            const bool store = !(flags & kFlagSkipStores);   // timing probe
+            const bool store = !(kTimingProbes && (flags & kFlagSkipStores));   // timing probe
             const uint32_t staging = staging_base + static_cast<uint32_t>(warp) * 8192u;
             if constexpr (S::kQuantOut) {
                 const int m_blk = w.a_row / kTileM, n_blk = w.blo_row / 128;
@@ -548,6 +549,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         tc_fence_after_sync();
         tmem_dealloc_pair(tmem_base, kTmemColumns);
     }
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.cycles) *p.cycles = static_cast<unsigned long long>(clock64() - launch_t0);
 }
 
 }  // namespace b200

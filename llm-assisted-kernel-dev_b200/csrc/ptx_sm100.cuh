@@ -110,7 +110,10 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
 // wake-up path of every wait that does not succeed at once.
 constexpr long long kWaitTimeoutCycles = 2000ll * 1000ll * 1000ll;
 
-template <bool kParked = false>
+// What the fault-injection self-test waits instead: about a millisecond.
+constexpr long long kShortWaitTimeoutCycles = 2ll * 1000ll * 1000ll;
+
+template <bool kParked = false, long long kLimit = kWaitTimeoutCycles>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -121,7 +124,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         for (int i = 0; i < 256; ++i)
             if (kParked ? mbar_try_wait_parked(bar, parity, 20000u) : mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitTimeoutCycles) {
+        if (clock64() - t0 > kLimit) {
             *abort_flag = 1u;
             atomicOr(status, code);
             return false;

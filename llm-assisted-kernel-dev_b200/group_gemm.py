@@ -21,6 +21,11 @@ from .formats import is_kernel_sf_layout
 # caches, group_gemm/group_gemm_cute5_v2.py:4319-4345).
 _plans: dict = {}
 _MAX_PLANS = 64
+# Workspaces of evicted plans, per (device, bytes).  They are never handed back to the
+# torch allocator while the library may still believe its descriptor table is in them:
+# eviction first tells the library to forget the address, then parks the tensor here for
+# the next plan of that size.
+_free_workspaces: dict = {}
 
 
 class _Plan:
@@ -62,8 +67,18 @@ def _build_plan(abc, sf_perm, sizes, validate: bool) -> _Plan:
         plan.sfa[i], plan.sfb[i] = sfa.data_ptr(), sfb.data_ptr()
         plan.mnk[3 * i], plan.mnk[3 * i + 1], plan.mnk[3 * i + 2] = m, n, k
     plan.ws_bytes = int(_lib.load().b200_grouped_workspace_bytes(g))
-    plan.workspace = torch.empty(plan.ws_bytes + 256, dtype=torch.uint8, device=dev)
+    pool = _free_workspaces.get((dev.index, plan.ws_bytes))
+    plan.workspace = pool.pop() if pool else torch.empty(plan.ws_bytes + 256, dtype=torch.uint8, device=dev)
     return plan
+
+
+def _workspace_ptr(plan: _Plan) -> int:
+    return (plan.workspace.data_ptr() + 255) & ~255
+
+
+def _evict(plan: _Plan) -> None:
+    _lib.check(_lib.load().b200_grouped_workspace_forget(plan.device, _workspace_ptr(plan)))
+    _free_workspaces.setdefault((plan.device, plan.ws_bytes), []).append(plan.workspace)
 
 
 def _signature(abc, sf_perm, sizes):
@@ -80,9 +95,9 @@ def grouped_gemm(abc_tensors, sfasfb_reordered_tensors, problem_sizes, *, varian
     if plan is None:
         plan = _build_plan(abc_tensors, sfasfb_reordered_tensors, problem_sizes, validate)
         if len(_plans) >= _MAX_PLANS:
-            _plans.pop(next(iter(_plans)))
+            _evict(_plans.pop(next(iter(_plans))))
         _plans[sig] = plan
-    ws_ptr = (plan.workspace.data_ptr() + 255) & ~255
+    ws_ptr = _workspace_ptr(plan)
     stream = torch.cuda.current_stream(plan.device).cuda_stream
     code = _lib.load().b200_grouped_gemm_nvfp4_ex(
         plan.g, plan.a, plan.b, plan.sfa, plan.sfb, plan.c, plan.mnk, ws_ptr, plan.ws_bytes, variant, tile_n,

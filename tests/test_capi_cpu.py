@@ -76,8 +76,20 @@ def test_dual_argument_errors(pkg, kw, code, needle):
 def test_dual_unknown_variant(pkg):
     lib = pkg._lib.load()
     p = [FAKE + 4096 * i for i in range(7)]
-    rc = lib.b200_dual_gemm_nvfp4_ex(*p, 128, 128, 256, 1, 128, 0, 0, 0, 99, None, 0, None, 0, None)
-    assert rc == pkg._lib.E_VARIANT
+    for variant in (-1, 9, 99, 100, 164, 400):     # the timing-probe range of instrumented builds included
+        rc = lib.b200_dual_gemm_nvfp4_ex(*p, 128, 128, 256, 1, 128, 0, 0, 0, variant, None, 0, None, 0, None)
+        assert rc == pkg._lib.E_VARIANT, variant
+
+
+def test_public_header_has_no_probe_variants():
+    text = open(os.path.join(ROOT, "include", "b200_nvfp4.h")).read()
+    assert "PROBE" not in text
+
+
+def test_forgetting_an_unknown_workspace_is_harmless(pkg):
+    lib = pkg._lib.load()
+    assert lib.b200_grouped_workspace_forget(0, FAKE) == 0
+    assert lib.b200_grouped_workspace_forget(3, None) == 0
 
 
 def _grouped(lib, mnk, ws=FAKE, ws_bytes=1 << 20, null_group=None, misalign=None, tile_n=0, variant=0):

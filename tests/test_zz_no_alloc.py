@@ -49,8 +49,16 @@ def _through_c_abi(pkg, data):
     pkg._lib.check(rc)
 
 
+def _oracle_problems(oracle, data, tol):
+    want = oracle.grouped_gemm(([tuple(t.cpu() for t in abc) for abc in data[0]], data[1]))
+    bad = []
+    for g, ((_a, _b, got), w) in enumerate(zip(data[0], want)):
+        bad += [(g, msg) for msg in oracle.compare(got, w, tol, tol)]
+    return bad
+
+
 @pytest.mark.gpu
-def test_static_table_entry_matches_workspace_entry_twice_in_a_row(pkg):
+def test_static_table_entry_matches_workspace_entry_twice_in_a_row(pkg, oracle):
     # two different problem lists back to back: the second call must not be
     # affected by the table entries the first one left behind
     cases = [([96, 0, 200, 130], [256, 128, 384, 512], [512, 256, 256, 768]),
@@ -59,7 +67,8 @@ def test_static_table_entry_matches_workspace_entry_twice_in_a_row(pkg):
     for seed, (m, n, k) in enumerate(cases):
         data = pkg.inputs.generate_grouped_input(m, n, k, len(m), 1111 + seed, dist="reference", device="cuda",
                                                  fill_c=100.0)
-        want = [c.clone() for c in pkg.group_gemm.custom_kernel(data)]     # existing entry point (workspace)
+        # existing entry point (workspace), on the same one-CTA kernels the static entry point runs
+        want = [c.clone() for c in pkg.group_gemm.custom_kernel(data, variant=pkg._lib.VARIANT_PERSISTENT)]
         torch.cuda.synchronize()
         for (_a, _b, c) in data[0]:
             c.fill_(-7.0)
@@ -72,6 +81,8 @@ def test_static_table_entry_matches_workspace_entry_twice_in_a_row(pkg):
                 continue
             diff = (got.float() - ref.float()).abs()
             assert torch.all(diff <= tol + tol * ref.float().abs()), (seed, g, diff.max().item())
+            assert torch.equal(got, ref), (seed, g)           # same kernel, same order of additions: same bits
+        assert _oracle_problems(oracle, data, tol) == []
     # the Python convenience wrapper takes the same route
     data = pkg.inputs.generate_grouped_input([136], [256], [512], 1, 5, dist="reference", device="cuda")
     want = pkg.group_gemm.custom_kernel(data)[0].clone()
@@ -79,3 +90,27 @@ def test_static_table_entry_matches_workspace_entry_twice_in_a_row(pkg):
     got = pkg.group_gemm.custom_kernel_no_alloc(data)[0]
     torch.cuda.synchronize()
     assert torch.equal(got, want)
+
+
+@pytest.mark.gpu
+def test_static_table_entry_allocates_nothing_and_serves_a_full_table(pkg, oracle):
+    # 64 groups (the table's capacity), four of them empty, wide enough that the entry point
+    # picks its 128 x 256 tiles: 60 groups x 2 x 8 tiles of 128 x 128 = 960 >= 4 per SM
+    g = pkg._lib.STATIC_MAX_GROUPS
+    m = [0 if i % 16 == 7 else 256 - (i % 5) * 24 for i in range(g)]
+    data = pkg.inputs.generate_grouped_input(m, [1024] * g, [256] * g, g, 77, dist="reference", device="cuda",
+                                             fill_c=100.0)
+    want = [c.clone() for c in pkg.group_gemm.custom_kernel(data, variant=pkg._lib.VARIANT_PERSISTENT, tile_n=256)]
+    _through_c_abi(pkg, data)                    # first call on this device may do the one-time set-up
+    torch.cuda.synchronize()
+    for (_a, _b, c) in data[0]:
+        c.fill_(-7.0)
+    before = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0])
+    _through_c_abi(pkg, data)
+    torch.cuda.synchronize()
+    after = (torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0])
+    assert after == before                       # neither torch's allocator nor the device lost a byte
+    assert pkg._lib.read_status(torch.cuda.current_device()) == 0
+    for i, ((_a, _b, got), ref) in enumerate(zip(data[0], want)):
+        assert torch.equal(got, ref), i
+    assert _oracle_problems(oracle, data, 1e-3) == []
