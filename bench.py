@@ -20,7 +20,15 @@ cpu_baseline / --impl reference
            the reference's fp32 dequantise-then-matmul CPU path (torch CPU ops,
            all host threads) on the same workload, a few passes
 extra      the other benchmark configurations (skinny-M dual GEMM, G=8 grouped
-           GEMM, 64-expert MoE grouped GEMM) in microseconds per launch
+           GEMM, 64-expert MoE grouped GEMM) in microseconds per launch; a block of
+           launches at least a second long ("sustained"); and, in a child process,
+           the reference's own sm_100a kernel and the cuBLASLt NVFP4 GEMM on the same GPU
+
+Timing protocol.  The reference times 15 or more data sets launched back to back between
+two CUDA events after one L2 flush, and stops when the error of the mean falls under 0.1 %
+(group_gemm/group_gemm_cute4.py:1586-1664, utils/dual_gemm/utils.py:165-172).  Here the
+step count is given on the command line, so the region is exactly K launches, and the L2
+is defeated by rotating input sets that together exceed it instead of one flush.
 """
 from __future__ import annotations
 
@@ -132,25 +140,100 @@ def cpu_reference_sample(steps: int, warmup: int):
     return flops / dt / 1e12, dt, torch.get_num_threads()
 
 
+def base_config():
+    """The `config` object, identical in both arms."""
+    return {"workload": WORKLOAD, "m": M, "n": N, "k": K, "l": 1,
+            "operands": "e2m1 codes uniform over 16 values, e4m3 scales U[0.25,2], seeds 0,42,.."}
+
+
 def run_reference(args):
+    """`--impl reference`: the reference's CPU path on the box's host cores, rank 0 only.  Every step is one
+    pass over the workload; when the requested steps would take more than a few minutes the passes run on
+    the first columns of the problem only (TFLOP/s does not depend on the width) and `sample` says so."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 10))
-    tflops, dt, threads = cpu_reference_sample(steps, max(1, min(args.warmup, 2)))
-    m, n, k = CPU_SAMPLE
-    sample = f"the whole workload per step: {m}x{n}x{k} (4*{m}*{n}*{k} flop), {steps} timed passes"
+    global CPU_SAMPLE
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    budget_passes = 150                       # about 0.9-1.5 s per full pass on 8-16 host cores
+    n_cols = N
+    if steps + warmup > budget_passes:
+        n_cols = max(128, (N * budget_passes // (steps + warmup)) // 128 * 128)
+    CPU_SAMPLE = (M, n_cols, K)
+    tflops, dt, threads = cpu_reference_sample(steps, warmup)
+    sample = (f"{'the whole workload' if n_cols == N else f'a problem {n_cols} instead of {N} columns wide'} per step: "
+              f"{M}x{n_cols}x{K} (4*{M}*{n_cols}*{K} flop), {steps} timed passes after {warmup} warm-up passes")
     line = {
         "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "warmup": warmup, "ms_per_step": dt * 1e3 * (N / n_cols), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 (dequantised e2m1 x e4m3)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "l": 1,
-                   "path": "reference CPU check: fp32 dequantise-then-matmul, silu*mul, fp16 cast (torch CPU ops)"},
+        "config": base_config(),
+        "details": {"path": "reference CPU check: fp32 dequantise-then-matmul, silu*mul, fp16 cast (torch CPU ops)"},
         "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- same-box comparison (child process)
+def run_same_box(args):
+    """`--same-box`: in a process of its own, time on this GPU (a) the reference's own sm_100a dual-GEMM
+    kernel, `custom_kernel` of dual_gemm/submission.py:894-957 (one CTA per 128 x 128 tile, CuTe DSL JIT),
+    and (b) the cuBLASLt NVFP4 GEMM behind `torch._scaled_mm` -- the library kernel the reference's
+    `ref_kernel` calls twice -- with the same event protocol as this library's figures.  Prints one JSON
+    object; a part that cannot run is reported as {"unavailable": reason}."""
+    import torch
+    pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import ref_loader
+    torch.cuda.set_device(0)
+    out = {}
+    shapes = {"dual_skinny_m256_n4096_k7168": (256, 4096, 7168), "dual_one_eighth_shard_m8192_n1792_k4096": (8192, 1792, 4096)}
+    steps, warmup = max(5, args.steps), max(3, args.warmup)
+
+    def timed(fn_for_set, n_sets):
+        sec, _, _ = time_launches(torch, lambda i: fn_for_set(i % n_sets), steps, warmup, lambda: None)
+        return sec / steps * 1e6
+
+    try:
+        if not ref_loader.available():
+            raise RuntimeError("baseline/_ref is not installed")
+        os.environ.setdefault("CUTE_DSL_ARCH", "sm_100a")
+        _ref, _specs, sub = ref_loader.load_dual(with_kernel=True)
+        k1 = {}
+        for name, (m, n, k) in shapes.items():
+            per_set = m * k // 2 + n * k
+            n_sets = max(2, min(8, -(-2 * L2_BYTES // per_set)))
+            sets = [pkg.inputs.generate_input(m, n, k, 1, 42 * i, dist="uniform16", device="cuda:0") for i in range(n_sets)]
+            sub.custom_kernel(sets[0])
+            torch.cuda.synchronize()
+            ours = pkg.dual_gemm.custom_kernel(tuple(t.clone() if t is not None else None for t in sets[0]))
+            torch.cuda.synchronize()
+            same = bool(torch.equal(torch.nan_to_num(ours.float(), 0.0, 1.0, -1.0).cpu(),
+                                    torch.nan_to_num(sets[0][9].float(), 0.0, 1.0, -1.0).cpu())) or None
+            us_ref = timed(lambda j: sub.custom_kernel(sets[j]), n_sets)
+            us_ours = timed(lambda j: pkg.dual_gemm.custom_kernel(sets[j]), n_sets)
+            k1[name] = {"reference_kernel_us": us_ref, "this_library_us": us_ours, "speedup": us_ref / us_ours,
+                        "bit_identical_outputs": same, "input_sets": n_sets}
+            del sets
+        out["reference_submission_kernel"] = k1
+    except Exception as exc:  # noqa: BLE001 - any import, JIT or launch failure is reported, not retried
+        out["reference_submission_kernel"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    try:
+        from oracle import nvfp4_oracle as orc
+        m, n, k = M, N, K
+        data = pkg.inputs.generate_input(m, n, k, 1, 0, dist="uniform16", device="cuda:0")
+        sa = orc.to_blocked(data[3][:, :, 0]).view(torch.float8_e4m3fn).cuda()
+        sb = orc.to_blocked(data[4][:, :, 0]).view(torch.float8_e4m3fn).cuda()
+        a2, b2 = data[0][:, :, 0], data[1][:, :, 0].transpose(0, 1)
+        us = timed(lambda j: torch._scaled_mm(a2, b2, sa, sb, bias=None, out_dtype=torch.float16), 1)
+        out["cublaslt_nvfp4_gemm"] = {"shape": [m, n, k], "us_per_gemm": us, "tflops": 2.0 * m * n * k / us / 1e6,
+                                      "note": "one plain block-scaled GEMM with fp16 output, no activation; the dual "
+                                              "GEMM is two of these plus silu*mul"}
+    except Exception as exc:  # noqa: BLE001
+        out["cublaslt_nvfp4_gemm"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    print(json.dumps(out), flush=True)
 
 
 # --------------------------------------------------------------------------- our arm (GPU)
@@ -244,7 +327,7 @@ def run_extra(torch, pkg, device, peaks, steps, warmup):
     us = sec / (steps * 4) * 1e6
     byts, flops = fmts.dual_gemm_bytes(m, n, k), fmts.dual_gemm_flops(m, n, k)
     extra["dual_skinny_m256_n4096_k7168"] = {
-        "us_per_launch": us, "tflops": flops / us / 1e6, "hbm_gbs": byts / us / 1e3,
+        "us_per_launch": us, "kernel": pkg._lib.last_kernel(), "tflops": flops / us / 1e6, "hbm_gbs": byts / us / 1e3,
         "frac_hbm_peak": byts / us / 1e3 / peaks["hbm_gbs"], "input_sets": 8}
     del sets
     # grouped GEMM, G=8, M_i ~ U{64..1024}, N=4096, K=7168: 2 input sets (2 x 140 MB > L2)
@@ -255,7 +338,8 @@ def run_extra(torch, pkg, device, peaks, steps, warmup):
     us = sec / (steps * 2) * 1e6
     sizes = gsets[0][3]
     byts, flops = fmts.grouped_gemm_bytes(sizes), fmts.grouped_gemm_flops(sizes)
-    extra["grouped_g8_n4096_k7168"] = {"us_per_launch": us, "m": ms, "tflops": flops / us / 1e6,
+    extra["grouped_g8_n4096_k7168"] = {"us_per_launch": us, "m": ms, "kernel": pkg._lib.last_kernel(),
+                                       "tflops": flops / us / 1e6,
                                        "hbm_gbs": byts / us / 1e3, "frac_hbm_peak": byts / us / 1e3 / peaks["hbm_gbs"]}
     del gsets
     # the benchmark dual GEMM with its result re-quantised to NVFP4 in the epilogue (input of a down projection)
@@ -278,6 +362,37 @@ def run_extra(torch, pkg, device, peaks, steps, warmup):
         extra[name] = {"us_per_launch": us, "hbm_gbs": qbytes / us / 1e3,
                        "frac_hbm_peak": qbytes / us / 1e3 / peaks["hbm_gbs"]}
         del xs
+    # the reference task's own benchmark shapes with its speed-of-light targets in microseconds
+    # (utils/dual_gemm/task.yml:33-38 and 59-62, utils/group_gemm/task.yml:35-39 and 59-62), reference distribution
+    task = {}
+    for (tm, tn, tk, sol) in ((256, 4096, 7168, 4.708), (512, 4096, 7168, 8.714), (256, 3072, 4096, 2.125),
+                              (512, 3072, 7168, 6.535)):
+        per_set = tm * tk // 2 + tn * tk
+        n_in = max(2, min(16, -(-2 * L2_BYTES // per_set)))
+        tsets = [pkg.inputs.generate_input(tm, tn, tk, 1, 1111 + 42 * i, dist="reference", device=device)
+                 for i in range(n_in)]
+        sec, _, _ = time_launches(torch, lambda i: pkg.dual_gemm.custom_kernel(tsets[i % n_in]), steps * 4, warmup,
+                                  lambda: None)
+        us = sec / (steps * 4) * 1e6
+        task[f"dual_m{tm}_n{tn}_k{tk}"] = {"us_per_launch": us, "speed_of_light_us": sol, "kernel": pkg._lib.last_kernel(),
+                                            "hbm_gbs": fmts.dual_gemm_bytes(tm, tn, tk) / us / 1e3, "input_sets": n_in}
+        del tsets
+    for (gm, gn, gk, sol) in (([80, 176, 128, 72, 64, 248, 96, 160], 4096, 7168, 18.833),
+                              ([40, 76, 168, 72, 164, 148, 196, 160], 7168, 2048, 10.667),
+                              ([192, 320], 3072, 4096, 2.406), ([128, 384], 4096, 1536, 1.525)):
+        g = len(gm)
+        per_set = g * gn * gk // 2
+        n_in = max(2, min(16, -(-2 * L2_BYTES // per_set)))
+        gsets = [pkg.inputs.generate_grouped_input(gm, [gn] * g, [gk] * g, g, 1111 + 42 * i, dist="reference",
+                                                   device=device) for i in range(n_in)]
+        sec, _, _ = time_launches(torch, lambda i: pkg.group_gemm.custom_kernel(gsets[i % n_in]), steps * 4, warmup,
+                                  lambda: None)
+        us = sec / (steps * 4) * 1e6
+        task[f"grouped_g{g}_n{gn}_k{gk}"] = {"us_per_launch": us, "speed_of_light_us": sol,
+                                             "kernel": pkg._lib.last_kernel(),
+                                             "hbm_gbs": fmts.grouped_gemm_bytes(gsets[0][3]) / us / 1e3, "input_sets": n_in}
+        del gsets
+    extra["reference_task_benchmarks"] = task
     # MoE grouped GEMM, 64 experts, 8192 tokens top-8 (sum M = 65536), N=2048, K=7168
     counts = pkg.inputs.moe_expert_counts(8192, 64, 8, seed=0)
     data = pkg.inputs.generate_grouped_input(counts, [2048] * 64, [7168] * 64, 64, 0, dist="uniform16", device=device)
@@ -285,7 +400,7 @@ def run_extra(torch, pkg, device, peaks, steps, warmup):
     us = sec / steps * 1e6
     byts, flops = fmts.grouped_gemm_bytes(data[3]), fmts.grouped_gemm_flops(data[3])
     extra["grouped_moe_g64_n2048_k7168"] = {
-        "us_per_launch": us, "m_min": min(counts), "m_max": max(counts), "zero_groups": counts.count(0),
+        "us_per_launch": us, "kernel": pkg._lib.last_kernel(), "m_min": min(counts), "m_max": max(counts), "zero_groups": counts.count(0),
         "tflops": flops / us / 1e6, "frac_fp4_nominal": flops / us / 1e6 / NOMINAL_FP4_TFLOPS,
         "hbm_gbs": byts / us / 1e3}
     return extra
@@ -326,26 +441,48 @@ def run_ours(args):
     launches0 = pkg._lib.launch_count()
     sampler = ClockSampler(local)
     sampler.start()
-    sec, t0, t1 = time_launches(torch, lambda i: pkg.dual_gemm.custom_kernel(dev_sets[i % n_sets]), args.steps,
-                                args.warmup, barrier)
-    clocks = sampler.stop(t0, t1)
-    launches = pkg._lib.launch_count() - launches0 - args.warmup
+    run_step = (lambda i: pkg.dual_gemm.custom_kernel(dev_sets[i % n_sets]))
+    # One region of exactly K launches on one GPU.  With several GPUs a K-launch region of a
+    # column shard lasts a millisecond or two and its max over ranks is dominated by jitter:
+    # the region is then timed five times and the median region is reported.
+    repeats = 1 if world == 1 else 5
+    regions = []
+    for rep in range(repeats):
+        sec, t0, t1 = time_launches(torch, run_step, args.steps, args.warmup if rep == 0 else 0, barrier)
+        t = torch.tensor([sec], dtype=torch.float64, device=device)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        regions.append((float(t.item()), sec, t0, t1))
+    regions.sort()
+    sec_max, sec, t0, t1 = regions[len(regions) // 2]
+    clocks = sampler.stop(min(r[2] for r in regions), max(r[3] for r in regions))
+    launches = (pkg._lib.launch_count() - launches0 - args.warmup) // repeats
+    kernel_name = pkg._lib.last_kernel()
     status = pkg._lib.read_status(local)
     if status:
         raise SystemExit(f"device status word {status:#x}: an on-device wait timed out")
-    t = torch.tensor([sec], dtype=torch.float64, device=device)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    sec_max = float(t.item())
     flops_total = 4.0 * M * N * K
     value = flops_total * args.steps / sec_max / 1e12
+
+    # SM clock this kernel really runs at: clock64 span of its first CTA / CUDA-event time of the same
+    # launch (nvidia-smi samples every 100 ms and cannot see a region of a few milliseconds)
+    eff = []
+    for i in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run_step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        eff.append(pkg._lib.last_launch_cycles(local) / (e0.elapsed_time(e1) * 1e3))
+    clocks["effective_sm_mhz"] = round(statistics.median(eff), 1)
+    clocks["effective_sm_mhz_how"] = "clock64 span of CTA 0 / CUDA-event time of the same launch, median of 5"
 
     if args.kernel_only:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                               "warmup": args.warmup, "ms_per_step": sec_max / args.steps * 1e3,
                               "config": {"workload": WORKLOAD}, "gpu_launches": int(launches), "clocks": clocks,
-                              "note": "kernel-only run for profiler captures"}), flush=True)
+                              "kernel": kernel_name, "note": "kernel-only run for profiler captures"}), flush=True)
         if dist is not None:
             dist.destroy_process_group()
         return
@@ -361,7 +498,14 @@ def run_ours(args):
     h_ops = [pin_bytes(x) for x in hs[:3]]
     h_sfs = [pin_sf(x) for x in hs[6:9]]
     h_c = torch.empty((1, M, n_local), dtype=torch.float16).pin_memory()
-    h2d = sum(x.numel() for x in h_ops + h_sfs)
+    # With several GPUs, A and its scale factors (the same on every rank) cross PCIe once, on rank 0,
+    # and reach the other ranks by an NCCL broadcast over NVLink; every rank uploads only its own rows
+    # of B1 / B2 and their scale factors.
+    shared_in = [h_ops[0], h_sfs[0]]
+    own_in = [h_ops[1], h_ops[2], h_sfs[1], h_sfs[2]]
+    shared_bytes = sum(x.numel() for x in shared_in)
+    own_bytes = sum(x.numel() for x in own_in)
+    h2d = shared_bytes + own_bytes if (dist is None or rank == 0) else own_bytes
     d2h = h_c.numel() * 2
     # Two device buffer sets and three streams: while step i computes, step i+1's inputs
     # arrive and step i-1's C leaves (PCIe is full duplex).  Every step still copies all
@@ -369,12 +513,15 @@ def run_ours(args):
     # kernel and copy-out in order.
     bufs = []
     for _ in range(2):
-        d_ops = [torch.empty_like(x, device=device) for x in h_ops]
-        d_sfs = [torch.empty_like(x, device=device) for x in h_sfs]
+        flat = torch.empty(shared_bytes, dtype=torch.uint8, device=device)      # A bytes, then SFA bytes
+        d_a = flat[:h_ops[0].numel()].view(h_ops[0].shape)
+        d_sfa = flat[h_ops[0].numel():].view(h_sfs[0].shape)
+        d_ops = [d_a] + [torch.empty_like(x, device=device) for x in h_ops[1:]]
+        d_sfs = [d_sfa] + [torch.empty_like(x, device=device) for x in h_sfs[1:]]
         d_c = torch.empty((1, M, n_local), dtype=torch.float16, device=device)
         d_data = tuple(x.permute(1, 2, 0).view(pkg.formats.FP4X2) for x in d_ops) + (None, None, None) + \
             tuple(x.permute(3, 4, 1, 5, 2, 0).view(torch.float8_e4m3fn) for x in d_sfs) + (d_c.permute(1, 2, 0),)
-        bufs.append({"ops": d_ops, "sfs": d_sfs, "c": d_c, "data": d_data, "in_done": torch.cuda.Event(),
+        bufs.append({"flat": flat, "ops": d_ops, "sfs": d_sfs, "c": d_c, "data": d_data, "in_done": torch.cuda.Event(),
                      "kernel_done": torch.cuda.Event(), "out_done": torch.cuda.Event()})
     s_in, s_run, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device), torch.cuda.Stream(device)
     e2e_steps = max(4, min(args.steps, 20))
@@ -383,8 +530,13 @@ def run_ours(args):
         b = bufs[i % 2]
         with torch.cuda.stream(s_in):
             s_in.wait_event(b["kernel_done"])          # the kernel that last read these inputs
-            for src, dst in zip(h_ops + h_sfs, b["ops"] + b["sfs"]):
+            if dist is None or rank == 0:
+                b["ops"][0].copy_(h_ops[0], non_blocking=True)
+                b["sfs"][0].copy_(h_sfs[0], non_blocking=True)
+            for src, dst in zip(own_in, [b["ops"][1], b["ops"][2], b["sfs"][1], b["sfs"][2]]):
                 dst.copy_(src, non_blocking=True)
+            if dist is not None:
+                dist.broadcast(b["flat"], src=0)       # ordered behind the copies above on this stream
             b["in_done"].record(s_in)
         with torch.cuda.stream(s_run):
             s_run.wait_event(b["in_done"])
@@ -418,15 +570,21 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = flops_total * e2e_steps / float(t.item()) / 1e12
 
-    # MoE grouped GEMM sharded by group (N > 1): every rank generates only the experts it owns
-    # (same seeds as the one-GPU list), no collective on the data path; time = max over ranks
+    io = torch.tensor([float(h2d), float(d2h)], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(io, op=dist.ReduceOp.SUM)      # bytes per step over all ranks
+    h2d_total, d2h_total = int(io[0].item()), int(io[1].item())
+
+    # MoE grouped GEMM sharded by group (N > 1): the one-GPU list (seed 0) is generated once on the host
+    # and every rank keeps the experts shard.shard_grouped_input gives it; no collective on the data
+    # path; time = max over ranks
     moe_sharded = None
     if dist is not None and not args.no_extra:
         counts = pkg.inputs.moe_expert_counts(8192, 64, 8, seed=0)
-        sizes = [(c_, 2048, 7168, 1) for c_ in counts]
-        mine = pkg.shard.assign_groups(sizes, world)[rank]
-        gdata = pkg.inputs.generate_grouped_input([counts[i] for i in mine], [2048] * len(mine), [7168] * len(mine),
-                                                  len(mine), 1000 + rank, dist="uniform16", device=device)
+        whole = pkg.inputs.generate_grouped_input(counts, [2048] * 64, [7168] * 64, 64, 0, dist="uniform16", device="cpu")
+        mine = pkg.shard.assign_groups(whole[3], world)[rank]
+        gdata = pkg.inputs.grouped_to_device(pkg.shard.shard_grouped_input(whole, rank, world), device)
+        del whole
         gsteps = max(5, min(args.steps, 50))
         gsec, _, _ = time_launches(torch, lambda i: pkg.group_gemm.custom_kernel(gdata), gsteps, 3, barrier)
         tg = torch.tensor([gsec], dtype=torch.float64, device=device)
@@ -434,12 +592,14 @@ def run_ours(args):
         us = float(tg.item()) / gsteps * 1e6
         total_flops = sum(2.0 * c_ * 2048 * 7168 for c_ in counts)
         moe_sharded = {"us_per_launch": us, "tflops": total_flops / us / 1e6, "groups_per_gpu": len(mine),
-                       "parallelism": f"64 experts sharded by group x{world}, no collective"}
+                       "kernel": pkg._lib.last_kernel(),
+                       "parallelism": f"64 experts (one seed-0 list) sharded by group x{world}, no collective"}
         del gdata
 
-    gather_ms = None
-    if args.gather and dist is not None:
-        # optional: full C on every rank (one NCCL all-gather of the column shards), outside the metric
+    gather_ms = gather_ok = None
+    if dist is not None:
+        # after the metric: full C on every rank (one NCCL all-gather of the column shards); the gathered
+        # matrix is checked against this rank's own shard
         shard_c = bufs[0]["c"].permute(1, 2, 0)
         for _ in range(2):
             pkg.shard.gather_dual_output(shard_c, N)
@@ -454,7 +614,29 @@ def run_ours(args):
         tg = torch.tensor([g0.elapsed_time(g1) / 5], dtype=torch.float64, device=device)
         dist.all_reduce(tg, op=dist.ReduceOp.MAX)
         gather_ms = float(tg.item())
-        assert tuple(full_c.shape) == (M, N, 1)
+        same = torch.equal(full_c[:, lo:hi].view(torch.int16), shard_c.view(torch.int16)) and \
+            tuple(full_c.shape) == (M, N, 1)
+        ok = torch.tensor([1.0 if same else 0.0], dtype=torch.float64, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        gather_ok = bool(ok.item() == 1.0)
+        del full_c
+
+    # a block of launches at least a second long: the power-capped regime a serving loop sees
+    sustained_block = None
+    if not args.no_extra:
+        n_long = max(args.steps, int(1.2 / (sec_max / args.steps)) + 1)
+        sampler = ClockSampler(local)
+        sampler.start()
+        lsec, lt0, lt1 = time_launches(torch, run_step, n_long, 0, barrier)
+        lclocks = sampler.stop(lt0, lt1)
+        t = torch.tensor([lsec], dtype=torch.float64, device=device)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        lval = flops_total * n_long / float(t.item()) / 1e12
+        sustained_block = {"value": lval, "unit": UNIT, "steps": n_long, "ms_per_step": float(t.item()) / n_long * 1e3,
+                           "clocks": lclocks,
+                           "frac_of_4x_bf16_sustained": lval / world / (4.0 * peaks["bf16_tflops_sustained"]),
+                           "frac_nominal": lval / world / NOMINAL_FP4_TFLOPS}
 
     if rank != 0:
         if dist is not None:
@@ -476,8 +658,14 @@ def run_ours(args):
                       f"{'power-capped' if sustained else 'not power-capped or short'}): no measured FP4 figure "
                       f"exists; nominal dense NVFP4 is {NOMINAL_FP4_TFLOPS:.0f}",
         "frac_of_burst_peak": achieved / (4.0 * peaks["bf16_tflops"]),
-        "frac_nominal": achieved / NOMINAL_FP4_TFLOPS, "kernel": "nvfp4_gemm_pair<PairDual>",
-        "avg_launch_us": sec / args.steps * 1e6, "traffic": TRAFFIC_BYTES_PER_LAUNCH if world == 1 else None,
+        "frac_nominal": achieved / NOMINAL_FP4_TFLOPS,
+        # An MMA-only loop of this library's instrumented build (every SM issuing 128x256x64 block-scaled
+        # MMAs back to back on random operand bytes, no loads, no epilogue) reached 8140-8190 TFLOP/s on this
+        # pool at 1.68 GHz (8850 with constant operands at 1.83 GHz): the ceiling for this data, below nominal.
+        "peak_mma_only": MMA_ONLY_TFLOPS, "frac_of_mma_only": achieved / MMA_ONLY_TFLOPS,
+        "kernel": kernel_name, "avg_launch_us": sec / args.steps * 1e6,
+        "traffic": TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and (M, N, K) == (8192, 14336, 4096)) else None,
+        "traffic_source": "one-pass ncu capture of a full-size launch, profiles/dual_gemm_pair_m8192_n14336_k4096_launches.md",
         "algorithmic_bytes": pkg.formats.dual_gemm_bytes(M, n_local, K),
     }
     line = {
@@ -485,19 +673,27 @@ def run_ours(args):
         "ms_per_step": sec_max / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3 block scale), f32 accumulate, f16 out",
         "data": "synthetic", "gpu_launches": int(launches),
-        "config": {"workload": WORKLOAD, "m": M, "n": N, "k": K, "l": 1, "n_per_gpu": n_local,
-                   "parallelism": f"column-sharded x{world}, A replicated, no collective",
-                   "operands": "e2m1 codes uniform over 16 values, e4m3 scales U[0.25,2], seeds 0,42,..",
-                   "l2": f"rotating {n_sets} input sets ({n_sets * per_set / 1e6:.0f} MB > L2 126 MB) plus "
-                         f"{2 * M * n_local / 1e6:.0f} MB of C written per step"},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                "steps": e2e_steps, "overlap": "copy-in, kernel and copy-out of consecutive steps on three streams"},
+        "config": base_config(),
+        "details": {"n_per_gpu": n_local, "parallelism": f"column-sharded x{world}, A replicated, no collective",
+                    "l2": f"rotating {n_sets} input sets ({n_sets * per_set / 1e6:.0f} MB > L2 126 MB) plus "
+                          f"{2 * M * n_local / 1e6:.0f} MB of C written per step",
+                    "timing": "one region of K launches" if repeats == 1 else
+                              f"median of {repeats} regions of K launches each (max over ranks per region); regions "
+                              f"in ms per step: {[round(r[0] / args.steps * 1e3, 4) for r in regions]}"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d_total, "d2h_bytes_per_step": d2h_total,
+                "steps": e2e_steps, "overlap": "copy-in, kernel and copy-out of consecutive steps on three streams",
+                "inputs": "every rank uploads its rows of B1/B2 and their scale factors" +
+                          ("" if world == 1 else "; A and its scale factors are uploaded on rank 0 and broadcast over NVLink (NCCL)")},
         "clocks": clocks, "roofline": roofline,
     }
+    extra = {}
     if gather_ms is not None:
         line["c_all_gather_ms"] = gather_ms
+        line["c_all_gather_matches_shards"] = gather_ok
     if moe_sharded is not None:
-        line["extra"] = {"grouped_moe_g64_n2048_k7168_sharded": moe_sharded}
+        extra["grouped_moe_g64_n2048_k7168_sharded"] = moe_sharded
+    if sustained_block is not None:
+        extra["sustained"] = sustained_block
     if world == 1:
         cpu_tflops, cpu_dt, threads = cpu_reference_sample(4, 1)
         m_, n_, k_ = CPU_SAMPLE
@@ -505,13 +701,33 @@ def run_ours(args):
                                 "sample": f"the whole workload ({m_}x{n_}x{k_}), 4 timed passes "
                                           f"({cpu_dt:.2f} s each)"}
         if not args.no_extra:
-            del dev_sets, host_sets
+            del dev_sets, host_sets, bufs
             torch.cuda.empty_cache()
-            line["extra"] = run_extra(torch, pkg, device, peaks, max(5, args.steps), max(3, args.warmup))
+            extra.update(run_extra(torch, pkg, device, peaks, max(5, min(args.steps, 200)), max(3, args.warmup)))
+            extra["same_gpu"] = same_box_child()
+    if extra:
+        line["extra"] = extra
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
+
+def same_box_child():
+    """Run `bench.py --same-box` in a child process (the reference's JIT-compiled kernel and the cuBLASLt
+    GEMM stay out of this process) and return its JSON object."""
+    try:
+        res = subprocess.run([sys.executable, os.path.abspath(__file__), "--same-box", "--steps", "30", "--warmup", "5"],
+                             capture_output=True, text=True, timeout=600, cwd=ROOT)
+        for ln in reversed(res.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                return json.loads(ln)
+        return {"unavailable": f"no JSON from the child (exit {res.returncode}): {res.stderr[-300:]}"}
+    except Exception as exc:  # noqa: BLE001
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+
+
+# TFLOP/s of an MMA-only loop on all SMs with random operand bytes (instrumented build, this pool)
+MMA_ONLY_TFLOPS = 8140.0
 
 # DRAM bytes (read + write) of one full-size dual-GEMM launch: dram__bytes_read.sum 85.6 MB +
 # dram__bytes_write.sum 194.6 MB from a one-pass ncu capture of `bench.py --kernel-only`
@@ -523,15 +739,15 @@ TRAFFIC_BYTES_PER_LAUNCH = 280.2e6
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=None, help="default: 1000 (GPU arm), 10 (reference arm)")
+    ap.add_argument("--warmup", type=int, default=None, help="default: 20 (GPU arm), 2 (reference arm)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--kernel-only", action="store_true",
                     help="only the device-timed launches (no e2e, CPU baseline or extras): for profiler captures")
     ap.add_argument("--shape", default=None, help="M,N,K override of the dual-GEMM shape (profiler captures)")
-    ap.add_argument("--gather", action="store_true",
-                    help="N > 1: also time one all-gather of the C shards after the timed region and report it")
+    ap.add_argument("--same-box", action="store_true",
+                    help="one GPU: time the reference's own sm_100a kernel and the cuBLASLt NVFP4 GEMM (child process of the default run)")
     ap.add_argument("--quantize", default=None, help="ROWS,K: launch only the activation quantiser (profiler captures)")
     ap.add_argument("--grouped", default=None, choices=["g8", "moe"],
                     help="launch only the G=8 or the 64-expert grouped GEMM (profiler captures, one GPU)")
@@ -540,9 +756,15 @@ def main():
         global M, N, K, WORKLOAD
         M, N, K = (int(x) for x in args.shape.split(","))
         WORKLOAD = f"dual_gemm_m{M}_n{N}_k{K}"
+    if args.steps is None:
+        args.steps = 10 if args.impl == "reference" else 1000
+    if args.warmup is None:
+        args.warmup = 2 if args.impl == "reference" else 20
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.same_box:
+        run_same_box(args)
     elif args.grouped:
         run_grouped_only(args)
     elif args.quantize:

@@ -234,6 +234,10 @@ int b200_read_status(int device, void* stream, uint32_t* out);
  * (group_gemm/group_gemm_cute4.py:67-79, 622-637). */
 int b200_read_last_cycles(int device, void* stream, uint64_t* out);
 
+/* Name of the kernel the most recent launch of this process used (which one the
+ * library's shape heuristic picked), e.g. "nvfp4_gemm_pair<PairDual>". */
+const char* b200_last_kernel(void);
+
 /* Number of kernels this library has launched in the calling process. */
 uint64_t b200_launch_count(void);
 

@@ -31,6 +31,7 @@ SIGNATURES = {
     "b200_version": (ctypes.c_char_p, []),
     "b200_last_error": (ctypes.c_char_p, []),
     "b200_launch_count": (ctypes.c_uint64, []),
+    "b200_last_kernel": (ctypes.c_char_p, []),
     "b200_dual_gemm_nvfp4": (_i, [_vp] * 7 + [_i] * 4 + [_i64, _vp, _i, _vp]),
     "b200_dual_gemm_nvfp4_ex": (_i, [_vp] * 7 + [_i] * 4 + [_i64] * 4 + [_i, _vp, _sz, _vp, _i, _vp]),
     "b200_dual_splitk_workspace_bytes": (_sz, [_i] * 4),
@@ -105,6 +106,10 @@ def last_launch_cycles(device: int, stream: int = 0) -> int:
     out = ctypes.c_uint64(0)
     check(load().b200_read_last_cycles(device, stream, ctypes.byref(out)))
     return int(out.value)
+
+
+def last_kernel() -> str:
+    return load().b200_last_kernel().decode()
 
 
 def launch_count() -> int:

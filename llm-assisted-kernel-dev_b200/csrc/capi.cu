@@ -21,6 +21,7 @@ thread_local std::string t_last_error;
 std::mutex g_mutex;
 uint64_t g_launches = 0;
 uint64_t g_epoch = 0;                  // split-k launches so far (their flag value)
+const char* g_last_kernel = "";       // name of the kernel the last launch used
 
 __device__ uint32_t g_device_status;   // library-owned status word (one per device)
 __device__ unsigned long long g_device_cycles;   // clock64 span of CTA 0 of the last GEMM launch (one per device)
@@ -244,6 +245,8 @@ int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStr
         <<<grid, kPersistentThreads, smem_bytes_persistent<M, kStages>(), stream>>>(prob, flags);
     B200_CUDA(cudaGetLastError());
     ++g_launches;
+    g_last_kernel = M == Mode::Dual ? "nvfp4_gemm_persistent<Dual>"
+                    : M == Mode::Group128 ? "nvfp4_gemm_persistent<Group128>" : "nvfp4_gemm_persistent<Group256>";
     return 0;
 }
 
@@ -267,6 +270,7 @@ int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, in
     cfg.numAttrs = 1;
     B200_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair<S, kTimingProbes>, prob, flags));
     ++g_launches;
+    g_last_kernel = S::kName;
     return 0;
 }
 int dual_pair_tiles(const DenseProblem& p) { return (p.m_tiles / 2) * p.n_tiles * p.batches; }
@@ -275,6 +279,7 @@ template <Mode M, typename P> int launch_serial(const P& prob, int units, int tw
     nvfp4_gemm_serial<M><<<units, 128, smem_bytes_serial<M>(), stream>>>(prob, two_mma);
     B200_CUDA(cudaGetLastError());
     ++g_launches;
+    g_last_kernel = "nvfp4_gemm_serial";
     return 0;
 }
 
@@ -290,6 +295,8 @@ const char* b200_version(void) { return "b200nvfp4 0.1 (sm_100a)"; }
 const char* b200_last_error(void) { return t_last_error.c_str(); }
 
 uint64_t b200_launch_count(void) { return g_launches; }
+
+const char* b200_last_kernel(void) { return g_last_kernel; }
 
 size_t b200_dual_splitk_workspace_bytes(int m, int n, int k, int l) {
     if (m <= 0 || n <= 0 || k <= 0 || l <= 0 || m % 128 || n % 128 || k % 256) return 0;
@@ -807,6 +814,7 @@ int b200_quantize_nvfp4(const void* x, int dtype, int rows, int k, int64_t ldx, 
     }
     B200_CUDA(cudaGetLastError());
     ++g_launches;
+    g_last_kernel = "nvfp4_quantize";
     return 0;
 }
 

@@ -49,6 +49,7 @@ constexpr uint32_t kStatusPairWait = 0x80;
 // Scheduling policies: work of one CTA (cluster rank) of the pair for pair tile `tile`.
 struct PairDual {
     using Params = DenseProblem;
+    static constexpr const char* kName = "nvfp4_gemm_pair<PairDual>";
     static constexpr bool kGrouped = false;
     static constexpr bool kQuantOut = false;
     __device__ static int total(const Params& p) { return (p.m_tiles / 2) * p.n_tiles * p.batches; }
@@ -91,11 +92,13 @@ struct PairDual {
 // Dual GEMM whose epilogue re-quantises its fp16 result to NVFP4 (packed e2m1 + e4m3
 // scale factors in the reordered layout), ready to be the A operand of the next GEMM.
 struct PairDualQuant : PairDual {
+    static constexpr const char* kName = "nvfp4_gemm_pair<PairDualQuant>";
     static constexpr bool kQuantOut = true;
 };
 
 struct PairGrouped {
     using Params = GroupedProblem;
+    static constexpr const char* kName = "nvfp4_gemm_pair<PairGrouped>";
     static constexpr bool kGrouped = true;
     static constexpr bool kQuantOut = false;
     __device__ static int total(const Params& p) { return p.total_tiles; }

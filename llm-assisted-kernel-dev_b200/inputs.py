@@ -147,6 +147,21 @@ def generate_grouped_input(m, n, k, g: int, seed: int, dist: str = "reference", 
     return (abc, sfs, sfs_perm, sizes)
 
 
+def grouped_to_device(data, device):
+    """Move a grouped 4-tuple generated on the CPU to ``device``, keeping every stride
+    (the un-reordered scale factors stay on the CPU, like the reference's)."""
+    abc, sfs, sfs_perm, sizes = data
+
+    def op(t):
+        return t.view(torch.uint8).permute(2, 0, 1).contiguous().to(device).permute(1, 2, 0).view(FP4X2)
+
+    def out(t):
+        return t.permute(2, 0, 1).contiguous().to(device).permute(1, 2, 0)
+    return ([(op(a), op(b), out(c)) for (a, b, c) in abc], list(sfs),
+            [(_to_device_keep_strides(x, device), _to_device_keep_strides(y, device)) for (x, y) in sfs_perm],
+            list(sizes))
+
+
 def moe_expert_counts(tokens: int, experts: int, top_k: int, seed: int) -> list[int]:
     """Tokens routed to each expert by top-k of softmax(N(0,1) logits); counts
     sum to tokens*top_k and may contain zeros."""

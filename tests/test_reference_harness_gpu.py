@@ -1,0 +1,73 @@
+"""The reference's own harness protocol judging this library's ``custom_kernel``:
+
+    data = generate_input(**spec); out = custom_kernel(clone(data)); check_implementation(data, out)
+
+(cholesky/eval.py:106-113) with the reference's ``generate_input`` drawing on CUDA, its
+``ref_kernel`` (``torch._scaled_mm``) as the expected value and its ``check_implementation``
+(rtol = atol = 1e-3, dual_gemm/reference.py:200) as the judge, on every test and benchmark
+spec of utils/dual_gemm/task.yml:46-62.  The reference files are taken, unmodified, from
+``baseline/_ref/`` (baseline/install_ref.py puts them there).  The grouped problem's
+``reference.py`` is not part of the reference checkout; its four benchmark lists
+(utils/group_gemm/task.yml:59-62) are run against the CPU oracle instead."""
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "baseline"))
+import ref_loader  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+DUAL_SPECS = 14
+GROUPED_BENCHMARKS = 4
+
+
+@pytest.fixture(scope="module")
+def reference_dual():
+    if not ref_loader.available():
+        pytest.skip("baseline/_ref is not installed (python baseline/install_ref.py)")
+    reference, specs = ref_loader.load_dual()
+    all_specs = list(specs["tests"]) + list(specs["benchmarks"])
+    assert len(all_specs) == DUAL_SPECS
+    return reference, all_specs
+
+
+def _clone(data):
+    # cholesky/eval.py:101-103 applied to every member of the tuple
+    return tuple(t.clone() if isinstance(t, torch.Tensor) else t for t in data)
+
+
+@pytest.mark.parametrize("index", range(DUAL_SPECS))
+def test_reference_check_implementation_accepts_custom_kernel(pkg, reference_dual, index):
+    reference, specs = reference_dual
+    spec = specs[index]
+    data = reference.generate_input(**spec)
+    torch.cuda.synchronize()
+    try:
+        expected = reference.ref_kernel(data)
+    except (RuntimeError, NotImplementedError, TypeError) as exc:
+        pytest.skip(f"the reference's ref_kernel does not run on this torch build: {str(exc)[:200]}")
+    del expected
+    out = pkg.dual_gemm.custom_kernel(_clone(data))
+    torch.cuda.synchronize()
+    assert pkg._lib.read_status(0) == 0
+    ok, message = reference.check_implementation(data, out)
+    assert ok, (spec, message)
+
+
+@pytest.mark.parametrize("index", range(GROUPED_BENCHMARKS))
+def test_grouped_benchmark_lists(pkg, oracle, index):
+    if not ref_loader.available():
+        pytest.skip("baseline/_ref is not installed (python baseline/install_ref.py)")
+    spec = ref_loader.grouped_specs()["benchmarks"][index]
+    data = pkg.inputs.generate_grouped_input(spec["m"], spec["n"], spec["k"], spec["g"], spec["seed"],
+                                             dist="reference", device="cuda", fill_c=100.0)
+    out = pkg.group_gemm.custom_kernel(data)
+    torch.cuda.synchronize()
+    assert pkg._lib.read_status(0) == 0
+    want = oracle.grouped_gemm(([tuple(t.cpu() for t in abc) for abc in data[0]], data[1]))
+    for g, (o, w) in enumerate(zip(out, want)):
+        assert oracle.compare(o, w, 1e-3, 1e-3) == [], (index, g)
