@@ -33,9 +33,11 @@ extern "C" {
                                  from host memory that dies when it returns      */
 
 /* Kernel variants (the `variant` argument of the *_ex entry points). */
-#define B200_VARIANT_AUTO 0       /* library picks by shape: PAIR for dual GEMMs with
-                                     m % 256 == 0 and at least two 128x128 tiles per SM,
-                                     else PERSISTENT                                    */
+#define B200_VARIANT_AUTO 0       /* library picks by shape.  Dual GEMM with m % 256 == 0:
+                                     PAIR_NARROW when all 256 x 64 tiles fit one round of
+                                     the GPU's CTA pairs, else PAIR (with a stream-k tail
+                                     when a workspace is given and whole tiles would leave
+                                     the last round under-filled); other m: PERSISTENT   */
 #define B200_VARIANT_PERSISTENT 1 /* warp-specialised persistent kernel               */
 #define B200_VARIANT_SERIAL 2     /* one CTA per tile, single stage (bring-up / debug) */
 #define B200_VARIANT_SERIAL_2MMA 3/* as SERIAL but two N=128 MMAs per k-block          */
@@ -45,6 +47,13 @@ extern "C" {
                                      needs m % 256 == 0.  Grouped GEMM: 256 x 256 tiles,
                                      needs every n % 256 == 0, any m                    */
 
+#define B200_VARIANT_PAIR_NARROW 6 /* dual GEMM: CTA pairs on 256 x 64 output tiles (2-SM MMA
+                                     256 x 128 x 64); for shapes with few tiles            */
+#define B200_VARIANT_PAIR_STREAMK 7 /* dual GEMM: PAIR whose last round and remainder are cut
+                                     along k so that every CTA pair gets the same number of
+                                     k-tiles; the two pairs that share a tile exchange fp32
+                                     partial sums through the workspace
+                                     (b200_dual_streamk_workspace_bytes)                   */
 #define B200_VARIANT_SELFTEST_LOST_LOAD 8 /* dual GEMM only, failure-detection self-test: the
                                      one-CTA kernel with its producer dropping the loads of
                                      every tile's second k-tile and every on-device wait
@@ -105,6 +114,14 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
                             int64_t sfb_batch_bytes, int variant, void* workspace,
                             size_t workspace_bytes, void* stream, int device, uint32_t* status);
 
+/* Bytes of scratch for the stream-k tail of the CTA-pair dual GEMM on a 148-SM B200
+ * (74 pairs x 256 KiB of fp32 partial sums plus flag words), or 0 when the shape's
+ * tiles fill whole rounds and nothing would be cut.  Pass it as `workspace` of
+ * b200_dual_gemm_nvfp4_ex: 256-byte aligned, zero-filled once before its first use,
+ * one workspace per stream.  AUTO uses it when cutting gains at least 3 %;
+ * without it whole tiles are dealt round-robin. */
+size_t b200_dual_streamk_workspace_bytes(int m, int n, int k, int l);
+
 /* Bytes of split-k workspace for an (m, n, k, l) problem on a 148-SM B200;
  * 0 when the shape has enough tiles and is not split. */
 size_t b200_dual_splitk_workspace_bytes(int m, int n, int k, int l);
@@ -141,8 +158,10 @@ int b200_grouped_gemm_nvfp4(int groups, const void* const* a, const void* const*
  * dies when the call returns, so a call that has to upload (first use of a
  * workspace, or changed arguments) is refused with B200_E_CAPTURE while `stream`
  * is being captured; a repeated call whose table is already in the workspace
- * only launches.  A repeated call on another stream than the one that uploaded
- * is ordered behind that upload with an event. */
+ * only launches.  The first repeated call on another stream than the one that
+ * uploaded makes that stream wait for the upload (an event), which a stream
+ * under capture cannot do: it is refused the same way.  So before capturing,
+ * make the call once, on the stream that will be captured. */
 int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* const* b,
                                const void* const* sfa, const void* const* sfb, void* const* c,
                                const int* mnk, void* workspace, size_t workspace_bytes, int variant,

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(HERE, "libb200nvfp4.so")
 
 VARIANT_AUTO, VARIANT_PERSISTENT, VARIANT_SERIAL, VARIANT_SERIAL_2MMA, VARIANT_SPLITK, VARIANT_PAIR = 0, 1, 2, 3, 4, 5
 
-VARIANT_SELFTEST_LOST_LOAD = 8
+VARIANT_PAIR_NARROW, VARIANT_PAIR_STREAMK, VARIANT_SELFTEST_LOST_LOAD = 6, 7, 8
 
 E_NULL, E_SHAPE, E_ALIGN, E_WORKSPACE, E_VARIANT, E_DRIVER, E_LIMIT, E_CAPTURE = -1, -2, -3, -4, -5, -6, -7, -8
 
@@ -35,6 +35,7 @@ SIGNATURES = {
     "b200_dual_gemm_nvfp4": (_i, [_vp] * 7 + [_i] * 4 + [_i64, _vp, _i, _vp]),
     "b200_dual_gemm_nvfp4_ex": (_i, [_vp] * 7 + [_i] * 4 + [_i64] * 4 + [_i, _vp, _sz, _vp, _i, _vp]),
     "b200_dual_splitk_workspace_bytes": (_sz, [_i] * 4),
+    "b200_dual_streamk_workspace_bytes": (_sz, [_i] * 4),
     "b200_grouped_gemm_nvfp4": (_i, [_i] + [_vp] * 6 + [_vp, _sz, _vp, _i, _vp]),
     "b200_grouped_gemm_nvfp4_ex": (_i, [_i] + [_vp] * 6 + [_vp, _sz, _i, _i, _vp, _i, _vp]),
     "b200_grouped_workspace_bytes": (_sz, [_i]),

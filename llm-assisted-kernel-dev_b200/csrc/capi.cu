@@ -1,6 +1,7 @@
 // Host side of libb200nvfp4.so: argument validation, tensor-map encoding,
 // launch configuration and the extern "C" entry points declared in
 // include/b200_nvfp4.h.  No torch types, no allocation of caller-visible memory.
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -70,15 +71,15 @@ int load_driver() {
     return 0;
 }
 
-// Packed e2m1 operand [batches][rows][k/2] bytes -> 3-D map, box 128 B x 128 rows,
+// Packed e2m1 operand [batches][rows][k/2] bytes -> 3-D map, box 128 B x box_rows rows,
 // 128-byte swizzle, out-of-range rows read as zero.
 int encode_operand_map(CUtensorMap* map, const void* base, int rows, int k, int batches,
-                       long long batch_stride_bytes) {
+                       long long batch_stride_bytes, unsigned box_rows = 128) {
     if (rows <= 0) rows = 1;   // empty group: never dereferenced, keep the encoder happy
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(rows),
                           static_cast<cuuint64_t>(batches)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(batch_stride_bytes)};
-    cuuint32_t box[3] = {128, 128, 1};
+    cuuint32_t box[3] = {128, box_rows, 1};
     cuuint32_t elem[3] = {1, 1, 1};
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, elem,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -119,7 +120,9 @@ template <typename K> int opt_in_smem(K kernel, uint32_t bytes) {
     return 0;
 }
 
-constexpr int B200_VARIANT_LAST = B200_VARIANT_SELFTEST_LOST_LOAD;
+constexpr int B200_VARIANT_LAST = B200_VARIANT_SELFTEST_LOST_LOAD;   // 6, 7: pair variants
+static_assert(pair_smem_bytes<PairDual>() <= 227u * 1024u && pair_smem_bytes<PairDualNarrow>() <= 227u * 1024u,
+              "shared memory budget of the pair kernels");
 constexpr int kDualStages = 4;
 constexpr int kG128Stages = 6;
 constexpr int kG256Stages = 4;
@@ -146,7 +149,7 @@ int device_state(int device, DeviceState** out) {
 #ifdef B200_TIMING_PROBES
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Dual, kDualStages, true>,
                               smem_bytes_persistent<Mode::Dual, kDualStages>()))) return rc;
-        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDual, true>, kPairSmemBytes))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDual, true>, pair_smem_bytes<PairDual>()))) return rc;
 #endif
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Dual, kDualStages, false, true>,
                               smem_bytes_persistent<Mode::Dual, kDualStages>()))) return rc;
@@ -154,9 +157,11 @@ int device_state(int device, DeviceState** out) {
                               smem_bytes_persistent<Mode::Group128, kG128Stages>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_persistent<Mode::Group256, kG256Stages>,
                               smem_bytes_persistent<Mode::Group256, kG256Stages>()))) return rc;
-        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDual>, kPairSmemBytes))) return rc;
-        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairGrouped>, kPairSmemBytes))) return rc;
-        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualQuant>, kPairSmemBytes))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDual>, pair_smem_bytes<PairDual>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualStreamK>, pair_smem_bytes<PairDualStreamK>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualNarrow>, pair_smem_bytes<PairDualNarrow>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairGrouped>, pair_smem_bytes<PairGrouped>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualQuant>, pair_smem_bytes<PairDualQuant>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Dual>, smem_bytes_serial<Mode::Dual>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group128>, smem_bytes_serial<Mode::Group128>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group256>, smem_bytes_serial<Mode::Group256>()))) return rc;
@@ -199,6 +204,8 @@ struct DualKey {
 struct DualMaps {
     DualKey key;
     CUtensorMap a, b1, b2, c;
+    CUtensorMap b1n, b2n;     // 64-row boxes, encoded on first use by the narrow pair kernel
+    bool has_narrow;
 };
 std::vector<DualMaps> g_dual_cache;   // small most-recently-used list
 
@@ -231,6 +238,20 @@ int split_count(int tiles, int k_tiles, int sms) {
     while (s > 1 && (s - 1) * ((k_tiles + s - 1) / s) >= k_tiles) --s;
     return s < 1 ? 1 : s;
 }
+// Pair tiles that go into the stream-k tail of a dual GEMM with `pair_tiles` 256 x 128 tiles of
+// `k_tiles` k-tiles on `pairs` CTA pairs: one round plus the remainder, when dealing whole tiles
+// would leave the last round under-filled (0 = whole tiles only).  `force` skips the 3 % threshold.
+int streamk_tiles(int pair_tiles, int k_tiles, int pairs, bool force) {
+    if (pairs <= 0 || pair_tiles <= pairs || k_tiles < 2) return 0;
+    const int rem = pair_tiles % pairs;
+    if (rem == 0) return 0;
+    const int full = pair_tiles / pairs;
+    const double exact = static_cast<double>(pair_tiles) / pairs;
+    if (!force && (full + 1 - exact) / exact < 0.03) return 0;
+    return pairs + rem;
+}
+size_t streamk_flag_bytes(int pairs) { return (static_cast<size_t>(pairs) * kStreamKFlagWords * 4 + 255) & ~static_cast<size_t>(255); }
+size_t streamk_bytes(int pairs) { return streamk_flag_bytes(pairs) + static_cast<size_t>(pairs) * kStreamKSlotFloats * 4; }
 size_t splitk_bytes(size_t tiles, int splits);
 size_t splitk_flag_bytes(size_t tiles) { return (tiles * 8 * sizeof(uint32_t) + 255) & ~static_cast<size_t>(255); }
 // epoch words (eight per tile) followed by the fp32 partial sums
@@ -259,7 +280,7 @@ int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, in
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     cfg.blockDim = dim3(320, 1, 1);
-    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.dynamicSmemBytes = pair_smem_bytes<S>();
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -297,6 +318,14 @@ const char* b200_last_error(void) { return t_last_error.c_str(); }
 uint64_t b200_launch_count(void) { return g_launches; }
 
 const char* b200_last_kernel(void) { return g_last_kernel; }
+
+size_t b200_dual_streamk_workspace_bytes(int m, int n, int k, int l) {
+    if (m <= 0 || n <= 0 || k <= 0 || l <= 0 || m % 256 || n % 128 || k % 256) return 0;
+    const long long pair_tiles = static_cast<long long>(m / 256) * (n / 128) * l;
+    if (pair_tiles > 100000000) return 0;
+    const int pairs = 148 / 2;
+    return streamk_tiles(static_cast<int>(pair_tiles), k / 256, pairs, true) > 0 ? streamk_bytes(pairs) : 0;
+}
 
 size_t b200_dual_splitk_workspace_bytes(int m, int n, int k, int l) {
     if (m <= 0 || n <= 0 || k <= 0 || l <= 0 || m % 128 || n % 128 || k % 256) return 0;
@@ -341,13 +370,14 @@ static int dual_gemm_impl(const void* a, const void* b1, const void* b2, const v
     DenseProblem p;
     memset(&p, 0, sizeof p);
     DualKey key{a, b1, b2, c, m, n, k, l, device, b_batch_bytes, ldc, c_batch, quant};
-    const DualMaps* maps = nullptr;
-    for (const DualMaps& e : g_dual_cache)
+    DualMaps* maps = nullptr;
+    for (DualMaps& e : g_dual_cache)
         if (e.key == key) { maps = &e; break; }
     if (!maps) {
         DualMaps fresh;
         memset(&fresh, 0, sizeof fresh);
         fresh.key = key;
+        fresh.has_narrow = false;
         if ((rc = encode_operand_map(&fresh.a, a, m, k, l, static_cast<long long>(m) * (k / 2)))) return rc;
         if ((rc = encode_operand_map(&fresh.b1, b1, n, k, l, b_batch_bytes))) return rc;
         if ((rc = encode_operand_map(&fresh.b2, b2, n, k, l, b_batch_bytes))) return rc;
@@ -411,14 +441,50 @@ static int dual_gemm_impl(const void* a, const void* b1, const void* b2, const v
     }
     if (p.k_splits > 1)
         return launch_persistent<Mode::Dual, kDualStages>(p, p.total_tiles * p.k_splits, st->sm_count, 0, s);
-    if (variant == B200_VARIANT_PAIR) {
-        if (p.m_tiles % 2) return fail(B200_E_SHAPE, "dual gemm: CTA pairs need m to be a multiple of 256 (m=%d)", m);
-        return launch_pair<PairDual>(p, dual_pair_tiles(p), st->sm_count, 0, s);
+    const bool wants_pair = variant == B200_VARIANT_PAIR || variant == B200_VARIANT_PAIR_NARROW ||
+                            variant == B200_VARIANT_PAIR_STREAMK;
+    if (wants_pair && p.m_tiles % 2)
+        return fail(B200_E_SHAPE, "dual gemm: CTA pairs need m to be a multiple of 256 (m=%d)", m);
+    // AUTO with row tiles that pair up: 256 x 64 tiles when that puts all of them into one round of the
+    // GPU's CTA pairs (shapes with few tiles: twice as many SMs stream the operands), else 256 x 128 tiles.
+    // Without pairing rows (m an odd multiple of 128) the one-CTA kernel runs.
+    const int pairs_avail = st->sm_count / 2;
+    const bool narrow = variant == B200_VARIANT_PAIR_NARROW ||
+                        (variant == B200_VARIANT_AUTO && p.m_tiles % 2 == 0 && p.total_tiles <= pairs_avail);
+    if (narrow) {
+        if (!maps->has_narrow) {
+            if ((rc = encode_operand_map(&maps->b1n, b1, n, k, l, b_batch_bytes, 64))) return rc;
+            if ((rc = encode_operand_map(&maps->b2n, b2, n, k, l, b_batch_bytes, 64))) return rc;
+            maps->has_narrow = true;
+        }
+        p.map_b1n = maps->b1n;
+        p.map_b2n = maps->b2n;
+        return launch_pair<PairDualNarrow>(p, p.total_tiles, st->sm_count, 0, s);
     }
-    // AUTO: CTA pairs when the row tiles pair up and every SM gets at least two tiles
-    // (with fewer the one-CTA kernel's finer tiles balance better).
-    if (variant == B200_VARIANT_AUTO && p.m_tiles % 2 == 0 && p.total_tiles >= 2 * st->sm_count)
-        return launch_pair<PairDual>(p, dual_pair_tiles(p), st->sm_count, 0, s);
+    if (wants_pair || (variant == B200_VARIANT_AUTO && p.m_tiles % 2 == 0)) {
+        // Stream-k tail: when whole tiles would leave the last round under-filled, the last round and the
+        // remainder are cut along k so that every pair gets the same number of k-tiles.  Needs scratch.
+        const int pair_tiles = dual_pair_tiles(p);
+        const int pairs = pairs_avail < pair_tiles ? pairs_avail : pair_tiles;
+        const int sk = variant == B200_VARIANT_PAIR ? 0
+                       : streamk_tiles(pair_tiles, p.k_tiles, pairs, variant == B200_VARIANT_PAIR_STREAMK);
+        if (sk > 0) {
+            const size_t need = streamk_bytes(pairs);
+            const bool usable = workspace && workspace_bytes >= need && !(reinterpret_cast<uintptr_t>(workspace) & 255u);
+            if (usable) {
+                p.sk_tiles = sk;
+                p.splitk_epoch = static_cast<uint32_t>(++g_epoch);     // a value no earlier launch has used;
+                if (p.splitk_epoch == 0) p.splitk_epoch = static_cast<uint32_t>(++g_epoch);   // the flags start at zero
+                p.splitk_flags = static_cast<uint32_t*>(workspace);
+                p.splitk_ws = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + streamk_flag_bytes(pairs));
+            } else if (variant == B200_VARIANT_PAIR_STREAMK) {
+                return fail(B200_E_WORKSPACE, "dual gemm: the stream-k tail needs a 256-byte aligned workspace of %zu bytes",
+                            need);
+            }
+        }
+        if (p.sk_tiles > 0) return launch_pair<PairDualStreamK>(p, pair_tiles, st->sm_count, 0, s);
+        return launch_pair<PairDual>(p, pair_tiles, st->sm_count, 0, s);
+    }
     switch (variant) {
         case B200_VARIANT_SERIAL:
             return launch_serial<Mode::Dual>(p, p.total_tiles, 0, s);
@@ -514,8 +580,8 @@ struct WorkspaceImage {
     std::vector<uint8_t> key;       // raw call arguments
     int total_tiles = 0;
     int tile_n = 0;
-    cudaStream_t upload_stream = nullptr;   // stream the table was copied on ...
-    cudaEvent_t uploaded = nullptr;         // ... and the event recorded behind that copy
+    cudaEvent_t uploaded = nullptr;         // recorded behind the copy of the table
+    std::vector<cudaStream_t> ordered;      // streams whose later work is ordered behind that copy
 };
 std::map<std::pair<int, const void*>, WorkspaceImage> g_workspaces;
 
@@ -534,8 +600,8 @@ int reject_capture(cudaStream_t s, const char* what) {
     if (e != cudaSuccess) return cuda_fail(e, "cudaStreamIsCapturing");
     if (cs != cudaStreamCaptureStatusNone)
         return fail(B200_E_CAPTURE,
-                    "%s: the stream is being captured and this call has to upload its descriptor table; "
-                    "make the call once outside the capture first", what);
+                    "%s: the stream is being captured and this call has to upload its descriptor table or wait "
+                    "for that upload; make the call once on this stream outside the capture first", what);
     return 0;
 }
 }  // namespace
@@ -626,13 +692,17 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
         B200_CUDA(cudaMemcpyAsync(workspace, table.data(), groups * sizeof(GroupEntry), cudaMemcpyHostToDevice, s));
         if (!img.uploaded) B200_CUDA(cudaEventCreateWithFlags(&img.uploaded, cudaEventDisableTiming));
         B200_CUDA(cudaEventRecord(img.uploaded, s));
-        img.upload_stream = s;
+        img.ordered.assign(1, s);
         img.key = key;
         img.total_tiles = total;
         img.tile_n = tile_n;
-    } else if (img.upload_stream != s) {
-        // same table, another stream: order this launch behind the copy that wrote it
+    } else if (std::find(img.ordered.begin(), img.ordered.end(), s) == img.ordered.end()) {
+        // Same table, first use on this stream: order the stream behind the copy that wrote the table.
+        // A stream under capture cannot wait for work outside its graph, so there the call is refused.
+        if ((rc = reject_capture(s, "grouped gemm (first use of this workspace on the stream)"))) return rc;
         B200_CUDA(cudaStreamWaitEvent(s, img.uploaded, 0));
+        if (img.ordered.size() >= 16) img.ordered.erase(img.ordered.begin() + 1);
+        img.ordered.push_back(s);
     }
     const WorkspaceImage& cur = g_workspaces[{device, workspace}];
     GroupedProblem p;

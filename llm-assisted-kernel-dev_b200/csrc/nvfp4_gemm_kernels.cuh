@@ -93,6 +93,7 @@ template <> struct ModeTraits<Mode::Group256> {
 struct alignas(64) DenseProblem {
     CUtensorMap map_a, map_b1, map_b2;   // 3-D {k/2 bytes, rows, batch}, box {128, 128, 1}
     CUtensorMap map_c;                   // 3-D {n, m, batch} fp16, box {64, 32, 1}, 128-byte swizzle (pair kernel)
+    CUtensorMap map_b1n, map_b2n;        // B1 / B2 with 64-row boxes (narrow pair tiles only)
     const uint8_t* sfa;
     const uint8_t* sfb1;
     const uint8_t* sfb2;
@@ -109,6 +110,7 @@ struct alignas(64) DenseProblem {
     int total_tiles;                     // m_tiles * n_tiles * batches
     int sf_k_atoms;                      // k / 64
     int k_splits;                        // 1 unless split-k
+    int sk_tiles;                        // pair kernel: pair tiles in the stream-k tail (0 = none)
     uint32_t* status;
     unsigned long long* cycles;          // CTA 0 stores its clock64 span here (one store per launch)
 };
@@ -447,10 +449,14 @@ __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base,
 // conflict-free for the 16-byte stores) and one lane hands each box to the TMA unit
 // as soon as its 64 columns are done.  `staging` is the warp's own area (1024-byte
 // aligned); a box is only rewritten after the previous tile's store has read it.
-template <int kBuf>
+// kAddPartial (stream-k head piece): `partial` points at this lane's slice of the fp32 partial
+// sums another CTA pair computed over the rest of the k range, laid out [4-column group][lane][4];
+// they are added to the accumulator values before the activation.
+template <int kBuf, bool kAddPartial = false>
 __device__ __forceinline__ void epilogue_tile_staged(const DenseProblem& p, const Work& w, uint32_t tmem_base,
                                                      int quad, int lane, uint32_t release_bar, uint32_t staging,
-                                                     int c_col, int c_row, bool store, Tracer* tr = nullptr) {
+                                                     int c_col, int c_row, bool store, Tracer* tr = nullptr,
+                                                     const float* partial = nullptr) {
     using TM = TmemMap<Mode::Dual>;
     constexpr int kEarly = TM::kEarlyChunks;
     constexpr int kSharedRel = (kBuf == 0) ? TM::kSharedBegin : 0;
@@ -490,6 +496,21 @@ __device__ __forceinline__ void epilogue_tile_staged(const DenseProblem& p, cons
         if (y_early) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) y[i] = early[(ycol - kSharedRel) / 16][i];
+        }
+        if constexpr (kAddPartial) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float4 px = ld_global_cg_v4f(partial + static_cast<size_t>(xcol / 4 + j) * 128);
+                const float4 py = ld_global_cg_v4f(partial + static_cast<size_t>(ycol / 4 + j) * 128);
+                x[4 * j] = __float_as_uint(__uint_as_float(x[4 * j]) + px.x);
+                x[4 * j + 1] = __float_as_uint(__uint_as_float(x[4 * j + 1]) + px.y);
+                x[4 * j + 2] = __float_as_uint(__uint_as_float(x[4 * j + 2]) + px.z);
+                x[4 * j + 3] = __float_as_uint(__uint_as_float(x[4 * j + 3]) + px.w);
+                y[4 * j] = __float_as_uint(__uint_as_float(y[4 * j]) + py.x);
+                y[4 * j + 1] = __float_as_uint(__uint_as_float(y[4 * j + 1]) + py.y);
+                y[4 * j + 2] = __float_as_uint(__uint_as_float(y[4 * j + 2]) + py.z);
+                y[4 * j + 3] = __float_as_uint(__uint_as_float(y[4 * j + 3]) + py.w);
+            }
         }
         uint32_t packed[8];
 #pragma unroll

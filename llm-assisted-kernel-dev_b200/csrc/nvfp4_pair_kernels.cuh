@@ -31,29 +31,56 @@
 
 namespace b200 {
 
-struct PairStage {
+// One pipeline stage of a CTA: its 128 rows of A, its kBRows rows of the merged B and the three
+// 2 KiB scale-factor chunks (SFA of its rows, SFB of both CTAs' B rows).
+template <int kBRows> struct PairStageT {
     static constexpr uint32_t kOffA = 0;
     static constexpr uint32_t kOffB = kOperandTileBytes;                 // this CTA's half of merged B
-    static constexpr uint32_t kOffSfA = 2 * kOperandTileBytes;
+    static constexpr uint32_t kOffSfA = kOperandTileBytes + kBRows * 128u;
     static constexpr uint32_t kOffSfB1 = kOffSfA + kSfChunkBytes;
     static constexpr uint32_t kOffSfB2 = kOffSfB1 + kSfChunkBytes;
-    static constexpr uint32_t kBytes = kOffSfB2 + kSfChunkBytes;        // 38 KiB, multiple of 1024
+    static constexpr uint32_t kBytes = kOffSfB2 + kSfChunkBytes;        // 38 KiB (128 rows) / 30 KiB (64 rows)
+    static_assert(kBytes % 1024 == 0, "stages keep the 1024-byte alignment of the swizzle atoms");
 };
-constexpr int kPairStages = 5;
 constexpr uint32_t kPairStagingBytes = 4u * 8192u;   // per epilogue warp: two boxes of 32 rows x 128 bytes
-constexpr uint32_t kPairSmemBytes =
-    1024u + kPairStages * PairStage::kBytes + kPairStagingBytes + sizeof(ControlBlock);
-static_assert(kPairSmemBytes <= 227u * 1024u, "shared memory budget");
+template <typename S> constexpr uint32_t pair_smem_bytes() {
+    return 1024u + S::kStages * PairStageT<S::kBRows>::kBytes + kPairStagingBytes + sizeof(ControlBlock);
+}
 constexpr uint32_t kStatusPairWait = 0x80;
 
+// Stream-k scratch of one pair: the fp32 accumulator of a 256 x 256 pair tile, laid out
+// [CTA rank][warp][4-column group][lane][4 floats] so that a warp's stores and loads are 512
+// contiguous bytes, and eight flag words (one per writing warp) per pair.
+constexpr size_t kStreamKSlotFloats = 2u * 4u * 64u * 32u * 4u;            // 65536 floats = 256 KiB
+constexpr size_t kStreamKFlagWords = 8;
+
+// One piece of work of a pair: k-tiles [kt_begin, kt_begin + kt_count) of pair tile `tile`.
+//   kind 0  the whole k range: ordinary epilogue
+//   kind 1  the tail of the k range (first piece of this pair's stream-k range): the fp32
+//           accumulator goes to the pair's scratch slot, nothing is stored to C
+//   kind 2  the head of the k range (last piece of the range): the next pair's slot is added
+//           to the accumulator before the epilogue
+struct PairPiece {
+    int tile, kt_begin, kt_count, kind;
+};
+
 // Scheduling policies: work of one CTA (cluster rank) of the pair for pair tile `tile`.
+//   kBRows   rows of the merged B that each CTA holds (the MMA's N is 2 * kBRows)
+//   kStages  pipeline depth that fits the shared memory beside the staging area
+//   TM       tensor-memory map (accumulator buffers, scale-factor ring)
 struct PairDual {
     using Params = DenseProblem;
+    using TM = TmemMap<Mode::Dual>;           // 256 accumulator columns per buffer, buffers overlap
     static constexpr const char* kName = "nvfp4_gemm_pair<PairDual>";
     static constexpr bool kGrouped = false;
     static constexpr bool kQuantOut = false;
+    static constexpr bool kStreamK = false;
+    static constexpr int kBRows = 128;
+    static constexpr int kMmaN = 256;
+    static constexpr int kStages = 5;
     __device__ static int total(const Params& p) { return (p.m_tiles / 2) * p.n_tiles * p.batches; }
     __device__ static int k_tiles(const Params& p, int /*tile*/, int& /*cursor*/) { return p.k_tiles; }
+    __device__ static int sfb_half(const Params& /*p*/, int /*tile*/) { return 0; }
     // rows of A/C are those of the CTA's rank, the B tile is B1 for rank 0 and B2 for rank 1
     __device__ static Work get(const Params& p, int tile, uint32_t rank, int& /*cursor*/) {
         const int m_pairs = p.m_tiles / 2;
@@ -86,9 +113,13 @@ struct PairDual {
     }
 };
 
-// Grouped: the host fills GroupEntry::m_tiles with the number of 256-row pair tiles
-// and n_tiles with n / 256; tiles are walked m-fastest inside a group like in the
-// one-CTA kernel, `cursor` remembers the group of the previous tile.
+// The same tiles with a stream-k tail (DenseProblem::sk_tiles > 0): a kernel of its own so that
+// the partial-sum code does not weigh on the registers of the plain one.
+struct PairDualStreamK : PairDual {
+    static constexpr const char* kName = "nvfp4_gemm_pair<PairDualStreamK>";
+    static constexpr bool kStreamK = true;
+};
+
 // Dual GEMM whose epilogue re-quantises its fp16 result to NVFP4 (packed e2m1 + e4m3
 // scale factors in the reordered layout), ready to be the A operand of the next GEMM.
 struct PairDualQuant : PairDual {
@@ -96,12 +127,73 @@ struct PairDualQuant : PairDual {
     static constexpr bool kQuantOut = true;
 };
 
+// Dual GEMM on 256 x 64 output tiles for shapes with few tiles (the reference task's
+// benchmark shapes have 48-128 tiles of 128 x 128 for 148 SMs): each CTA holds 64 rows of
+// B1 (rank 0) or of B2 (rank 1), the MMA is 256 x 128 x 64, accumulator columns [0,64) =
+// A.B1^T and [64,128) = A.B2^T.  Twice as many pair tiles as PairDual, 30 KiB instead of
+// 38 KiB of loads and 24 KiB instead of 32 KiB of MMA operand reads per k-tile and CTA.
+// The scale factors of 64 B rows are half of a 128-row atom: the whole atom is loaded and
+// the scale-factor warps pick the two 32-row groups of their tile (`sfb_half`).
+struct PairDualNarrow {
+    using Params = DenseProblem;
+    using TM = TmemMap<Mode::Group128>;       // two disjoint 128-column accumulators
+    static constexpr const char* kName = "nvfp4_gemm_pair<PairDualNarrow>";
+    static constexpr bool kGrouped = false;
+    static constexpr bool kQuantOut = false;
+    static constexpr bool kStreamK = false;
+    static constexpr int kBRows = 64;
+    static constexpr int kMmaN = 128;
+    static constexpr int kStages = 6;
+    __device__ static int total(const Params& p) { return (p.m_tiles / 2) * p.n_tiles * 2 * p.batches; }
+    __device__ static int k_tiles(const Params& p, int /*tile*/, int& /*cursor*/) { return p.k_tiles; }
+    __device__ static int n_blk64(const Params& p, int tile) { return (tile / (p.m_tiles / 2)) % (p.n_tiles * 2); }
+    __device__ static int sfb_half(const Params& p, int tile) { return n_blk64(p, tile) & 1; }
+    __device__ static Work get(const Params& p, int tile, uint32_t rank, int& /*cursor*/) {
+        const int m_pairs = p.m_tiles / 2;
+        const int m_pair = tile % m_pairs;
+        const int t = tile / m_pairs;
+        const int n64 = t % (p.n_tiles * 2);
+        const int b = t / (p.n_tiles * 2);
+        const int m_blk = 2 * m_pair + static_cast<int>(rank);
+        Work w;
+        w.map_a = &p.map_a;
+        w.map_blo = rank == 0 ? static_cast<const void*>(&p.map_b1n) : static_cast<const void*>(&p.map_b2n);
+        w.map_bhi = w.map_blo;
+        w.a_row = m_blk * kTileM;
+        w.blo_row = w.bhi_row = n64 * 64;
+        w.batch = b;
+        const long long sf_row = static_cast<long long>(p.sf_k_atoms) * kSfAtomBytes;
+        w.sfa = p.sfa + b * p.sfa_batch + m_blk * sf_row;
+        w.sfblo = p.sfb1 + b * p.sfb_batch + (n64 >> 1) * sf_row;
+        w.sfbhi = p.sfb2 + b * p.sfb_batch + (n64 >> 1) * sf_row;
+        w.ldc = p.ldc;
+        w.c = p.c + b * p.c_batch + static_cast<long long>(m_blk) * kTileM * p.ldc + n64 * 64;
+        w.rows_valid = kTileM;
+        w.cols_valid = 64;
+        w.k_tile_begin = 0;
+        w.k_tile_count = p.k_tiles;
+        w.group = 0;
+        w.tile = tile;
+        w.split = 0;
+        return w;
+    }
+};
+
+// Grouped: the host fills GroupEntry::m_tiles with the number of 256-row pair tiles
+// and n_tiles with n / 256; tiles are walked m-fastest inside a group like in the
+// one-CTA kernel, `cursor` remembers the group of the previous tile.
 struct PairGrouped {
     using Params = GroupedProblem;
+    using TM = TmemMap<Mode::Group256>;
     static constexpr const char* kName = "nvfp4_gemm_pair<PairGrouped>";
     static constexpr bool kGrouped = true;
     static constexpr bool kQuantOut = false;
+    static constexpr bool kStreamK = false;
+    static constexpr int kBRows = 128;
+    static constexpr int kMmaN = 256;
+    static constexpr int kStages = 5;
     __device__ static int total(const Params& p) { return p.total_tiles; }
+    __device__ static int sfb_half(const Params& /*p*/, int /*tile*/) { return 0; }
     __device__ static const GroupEntry* find(const Params& p, int tile, int& cursor) {
         int g = cursor;
         const GroupEntry* e = p.groups + g;
@@ -141,6 +233,59 @@ struct PairGrouped {
         w.tile = tile;
         w.split = 0;
         return w;
+    }
+};
+
+// The sequence of pieces of one pair, the same in every role of both CTAs.  Whole tiles are
+// dealt round-robin (tile = pair, pair + pairs, ...).  With a stream-k tail (PairDual,
+// sk_tiles > 0) only the first total - sk_tiles tiles are dealt that way (a whole number of
+// rounds); the k-tiles of the last sk_tiles tiles form one line of sk_tiles * k_tiles units
+// that is cut into `pairs` equal ranges, so every pair gets the same amount of work to the
+// k-tile.  A range is at least one tile long (the host guarantees sk_tiles >= pairs), so a
+// tile is shared by at most two neighbouring pairs: pair i runs its head (k-tiles from 0) at the
+// end of its range, pair i + 1 its tail at the start of its own.  The tail's accumulator goes
+// through pair i + 1's scratch slot, long before pair i asks for it.
+template <typename S> struct PairWalk {
+    int pairs, dp_tiles, next_dp, k_tiles;
+    long long u, u_end;
+    __device__ PairWalk(const typename S::Params& p, int pair, int pairs_) : pairs(pairs_), k_tiles(1), u(0), u_end(0) {
+        const int total = S::total(p);
+        dp_tiles = total;
+        next_dp = pair;
+        if constexpr (S::kStreamK) {
+            if (p.sk_tiles > 0) {
+                dp_tiles = total - p.sk_tiles;
+                k_tiles = p.k_tiles;
+                const long long units = static_cast<long long>(p.sk_tiles) * p.k_tiles;
+                u = units * pair / pairs;
+                u_end = units * (pair + 1) / pairs;
+            }
+        }
+    }
+    __device__ bool next(const typename S::Params& p, int& cursor, PairPiece& out) {
+        if (next_dp < dp_tiles) {
+            out.tile = next_dp;
+            out.kt_begin = 0;
+            out.kt_count = S::k_tiles(p, next_dp, cursor);
+            out.kind = 0;
+            next_dp += pairs;
+            return true;
+        }
+        if constexpr (S::kStreamK) {
+            if (u < u_end) {
+                const int t = static_cast<int>(u / k_tiles);
+                const int kt0 = static_cast<int>(u - static_cast<long long>(t) * k_tiles);
+                const long long left = u_end - u;
+                const int cnt = (k_tiles - kt0) < left ? (k_tiles - kt0) : static_cast<int>(left);
+                out.tile = dp_tiles + t;
+                out.kt_begin = kt0;
+                out.kt_count = cnt;
+                out.kind = kt0 > 0 ? 1 : (cnt < k_tiles ? 2 : 0);
+                u += cnt;
+                return true;
+            }
+        }
+        return false;
     }
 };
 
@@ -270,27 +415,118 @@ __device__ __forceinline__ void epilogue_tile_quant(const DenseProblem& p, const
     }
 }
 
+// Narrow dual tile (PairDualNarrow), one warp: 32 rows x 64 output columns.  Accumulator
+// columns [0,64) = x, [64,128) = y; the fp16 results go through one swizzled 4 KiB box of the
+// warp's staging area and leave with one TMA store.
+template <int kBuf>
+__device__ __forceinline__ void epilogue_tile_narrow(const DenseProblem& p, const Work& w, uint32_t tmem_base, int quad,
+                                                     int lane, uint32_t staging, int c_col, int c_row, bool store) {
+    using TM = TmemMap<Mode::Group128>;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
+    if (lane == 0) bulk_wait_group_read_all();      // the previous tile's box has left the staging area
+    __syncwarp();
+    const uint32_t row_base = staging + lane * 128;
+    const uint32_t swz = static_cast<uint32_t>(lane & 7);
+#pragma unroll
+    for (int chunk = 0; chunk < 4; ++chunk) {
+        uint32_t x[16], y[16];
+        tc_ld_x16(acc + chunk * 16, x);
+        tc_ld_x16(acc + 64 + chunk * 16, y);
+        tc_wait_ld();
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            packed[i] = pack_half2(silu_mul(__uint_as_float(x[2 * i]), __uint_as_float(y[2 * i])),
+                                   silu_mul(__uint_as_float(x[2 * i + 1]), __uint_as_float(y[2 * i + 1])));
+        const uint32_t u0 = static_cast<uint32_t>(chunk * 2);
+        st_shared_v4(row_base + ((u0 ^ swz) << 4), packed[0], packed[1], packed[2], packed[3]);
+        st_shared_v4(row_base + (((u0 + 1) ^ swz) << 4), packed[4], packed[5], packed[6], packed[7]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && store) {
+        tma_store_3d(&p.map_c, staging, c_col, c_row, w.batch);
+        bulk_commit_group();
+    }
+}
+
+// Stream-k, tail piece: this warp's 32 rows x 256 accumulator columns go to the pair's scratch
+// slot as fp32; nothing is stored to C.  The columns shared with the other accumulator buffer
+// are read first and the buffer is handed back before the rest is copied.
+template <int kBuf>
+__device__ __forceinline__ void epilogue_partial_store(const DenseProblem& p, uint32_t tmem_base, uint32_t rank,
+                                                       int quad, int lane, uint32_t release_bar, int slot) {
+    using TM = TmemMap<Mode::Dual>;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
+    float* dst = p.splitk_ws + static_cast<size_t>(slot) * kStreamKSlotFloats +
+                 static_cast<size_t>(rank * 4 + quad) * (64 * 128) + lane * 4;
+    // buffer 0 shares its columns [112,256), buffer 1 its columns [0,144)
+    constexpr int kFirst = (kBuf == 0) ? 112 : 0;
+#pragma unroll 1
+    for (int i = 0; i < 16; ++i) {
+        const int col = (kFirst + i * 16) & 255;
+        uint32_t v[16];
+        tc_ld_x16(acc + col, v);
+        tc_wait_ld();
+        if (i == 8) {                              // the 144 shared columns are in registers or memory
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster_relaxed(release_bar);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            st_global_v4f(dst + static_cast<size_t>(col / 4 + j) * 128, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    }
+    __threadfence();
+    __syncwarp();
+    if (lane == 0)
+        st_release_gpu_u32(p.splitk_flags + static_cast<size_t>(slot) * kStreamKFlagWords + rank * 4 + quad,
+                           p.splitk_epoch);
+}
+
+// Stream-k, head piece: wait (bounded) until the warp with the same rows in the pair that ran the
+// tail of this tile has published its partial sums.
+__device__ __forceinline__ bool wait_partial(const DenseProblem& p, int slot, uint32_t rank, int quad,
+                                             volatile uint32_t* abort_flag) {
+    const uint32_t* flag = p.splitk_flags + static_cast<size_t>(slot) * kStreamKFlagWords + rank * 4 + quad;
+    bool ok = true;
+    if (ld_acquire_gpu_u32(flag) != p.splitk_epoch) {
+        const long long t0 = clock64();
+        while (ld_acquire_gpu_u32(flag) != p.splitk_epoch) {
+            if (*abort_flag || clock64() - t0 > kWaitTimeoutCycles) {
+                *abort_flag = 1u;
+                atomicOr(p.status, kStatusSplitKWait);
+                ok = false;
+                break;
+            }
+            __nanosleep(200);
+        }
+    }
+    return __all_sync(0xffffffffu, ok);
+}
+
 template <typename S, bool kTimingProbes = false>
 __global__ void __launch_bounds__(320, 1)
 nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
-    using TM = TmemMap<Mode::Dual>;          // same TMEM map for both: 256 accumulator columns per buffer
-    using T = ModeTraits<Mode::Dual>;
-    static_assert(TmemMap<Mode::Group256>::kAccStride == TM::kAccStride, "one TMEM map for both pair kernels");
+    using TM = typename S::TM;
+    using Stage = PairStageT<S::kBRows>;
+    constexpr int kStages = S::kStages;
+    constexpr int kWordsPerBlock = TM::kSlotCols;          // scale-factor words per 64-k block and lane
+    static_assert(kWordsPerBlock == 4 + S::kMmaN / 32, "scale-factor slot = SFA 4 columns + SFB N/32 columns");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     ControlBlock* ctl = reinterpret_cast<ControlBlock*>(smem_raw + (smem_base - smem_u32(smem_raw)) +
-                                                        kPairStages * PairStage::kBytes + kPairStagingBytes);
-    const uint32_t staging_base = smem_base + kPairStages * PairStage::kBytes;
+                                                        kStages * Stage::kBytes + kPairStagingBytes);
+    const uint32_t staging_base = smem_base + kStages * Stage::kBytes;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = cluster_cta_rank();          // 0: issues the MMAs, 1: partner
     const int pair = blockIdx.x >> 1;
     const int pairs = gridDim.x >> 1;
-    const int total = S::total(p);
     const long long launch_t0 = clock64();
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kPairStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
             mbar_init(smem_u32(&ctl->empty[s]), 1);
         }
@@ -300,7 +536,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         }
         // one hand-over barrier per stage: a slot is reused only after the MMA thread
         // passed its previous use (the stage had to be freed in between); used in CTA 0
-        for (int i = 0; i < kPairStages; ++i) mbar_init(smem_u32(&ctl->sf_ready[i]), 8);
+        for (int i = 0; i < kStages; ++i) mbar_init(smem_u32(&ctl->sf_ready[i]), 8);
         mbar_init(smem_u32(&ctl->aux[0]), 1);
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -322,29 +558,36 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         // ------------------------------ scale factors: own shared memory -> own TMEM
         const uint32_t quad_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
         constexpr uint32_t kUnitsPerKTile = kKBlocks / TM::kGranule;
+        constexpr int kUnitWords = TM::kGranule * kWordsPerBlock;   // 24 (N = 256) or 32 (N = 128)
         uint32_t s = 0, ph = 0, kt = 0, buf = 0, units = 0, retired = 0, rs = 0, rph = 0;
         bool ok = true;
-        Tracer trace(nullptr, 0);
         int cursor = 0;
-        for (int tile = pair; ok && tile < total; tile += pairs) {
-            const int k_tiles = S::k_tiles(p, tile, cursor);
-            for (int i = 0; ok && i < k_tiles; ++i) {
+        PairWalk<S> walk(p, pair, pairs);
+        PairPiece pc;
+        while (ok && walk.next(p, cursor, pc)) {
+            const uint32_t half_off = static_cast<uint32_t>(S::sfb_half(p, pc.tile)) * 8u;
+            for (int i = 0; ok && i < pc.kt_count; ++i) {
                 if (!mbar_wait<true>(smem_u32(&ctl->full[s]), ph, abort_flag, p.status, kStatusSfWait)) {
                     ok = false;
                     break;
                 }
-                trace(1);   // operands landed
-                uint32_t v[kKBlocks * 12];
-                const uint32_t src = smem_base + s * PairStage::kBytes + lane * 16;
+                uint32_t v[kKBlocks * kWordsPerBlock];
+                const uint32_t src = smem_base + s * Stage::kBytes + lane * 16;
                 if (!(kTimingProbes && (flags & kFlagSkipBHi)))   // timing probe (bit reused): no scale-factor reads
 #pragma unroll
                 for (int kb = 0; kb < kKBlocks; ++kb) {
-                    uint32_t* d = v + kb * 12;
-                    ld_shared_v4(src + PairStage::kOffSfA + kb * kSfAtomBytes, d[0], d[1], d[2], d[3]);
-                    ld_shared_v4(src + PairStage::kOffSfB1 + kb * kSfAtomBytes, d[4], d[5], d[6], d[7]);
-                    ld_shared_v4(src + PairStage::kOffSfB2 + kb * kSfAtomBytes, d[8], d[9], d[10], d[11]);
+                    uint32_t* d = v + kb * kWordsPerBlock;
+                    ld_shared_v4(src + Stage::kOffSfA + kb * kSfAtomBytes, d[0], d[1], d[2], d[3]);
+                    if constexpr (S::kMmaN == 256) {
+                        ld_shared_v4(src + Stage::kOffSfB1 + kb * kSfAtomBytes, d[4], d[5], d[6], d[7]);
+                        ld_shared_v4(src + Stage::kOffSfB2 + kb * kSfAtomBytes, d[8], d[9], d[10], d[11]);
+                    } else {
+                        // 64 B rows per CTA: two of the atom's four 32-row groups
+                        ld_shared_v2(src + Stage::kOffSfB1 + kb * kSfAtomBytes + half_off, d[4], d[5]);
+                        ld_shared_v2(src + Stage::kOffSfB2 + kb * kSfAtomBytes + half_off, d[6], d[7]);
+                    }
                 }
-                // ring units of this k-tile were last read by k-tile (units + 1 - kBuffers) / 2
+                // ring units of this k-tile were last read by k-tile (units + 1 - kBuffers) / kUnitsPerKTile
                 const uint32_t last_unit = units + kUnitsPerKTile - 1;
                 const bool probe_skip = kTimingProbes && (flags & kFlagSkipSfCopy) && kt >= 2;   // timing probe
                 if (!probe_skip && last_unit >= static_cast<uint32_t>(TM::kBuffers)) {
@@ -352,25 +595,25 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     if (retired <= need) {
                         while (retired < need) {
                             ++retired;
-                            if (++rs == kPairStages) { rs = 0; rph ^= 1u; }
+                            if (++rs == kStages) { rs = 0; rph ^= 1u; }
                         }
                         // arrived on by the first CTA's tcgen05.commit
                         ok = mbar_wait<false>(smem_u32(&ctl->empty[rs]), rph, abort_flag, p.status, kStatusSfWait);
                         ++retired;
-                        if (++rs == kPairStages) { rs = 0; rph ^= 1u; }
+                        if (++rs == kStages) { rs = 0; rph ^= 1u; }
                         if (!ok) break;
                         tc_fence_after_sync();
                     }
                 }
-                trace(2);   // ring units free
                 if (!probe_skip) {
 #pragma unroll
                     for (int gr = 0; gr < static_cast<int>(kUnitsPerKTile); ++gr) {
                         uint32_t b = buf + gr;
                         if (b >= static_cast<uint32_t>(TM::kBuffers)) b -= TM::kBuffers;
                         const uint32_t dst = tmem_base + quad_lane + TM::sfa_col(b * TM::kGranule);
-                        tc_st_x16(dst, v + gr * 24);
-                        tc_st_x8(dst + 16, v + gr * 24 + 16);
+                        tc_st_x16(dst, v + gr * kUnitWords);
+                        if constexpr (kUnitWords == 24) tc_st_x8(dst + 16, v + gr * kUnitWords + 16);
+                        else tc_st_x16(dst + 16, v + gr * kUnitWords + 16);
                     }
                     tc_wait_st();
                 }
@@ -380,9 +623,8 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ctl->sf_ready[s]), 0));
-                trace(3);   // handed to the MMA thread
                 ++kt;
-                if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                if (++s == kStages) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 5) {
@@ -390,37 +632,38 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            Tracer trace(nullptr, 0);
             int cursor = 0, last_group = -1;
-            for (int tile = pair; ok && tile < total; tile += pairs) {
-                const Work w = S::get(p, tile, rank, cursor);
+            PairWalk<S> walk(p, pair, pairs);
+            PairPiece pc;
+            while (ok && walk.next(p, cursor, pc)) {
+                const Work w = S::get(p, pc.tile, rank, cursor);
                 if (S::kGrouped && w.group != last_group) {   // tensor maps of a new group, written by the host
                     tensormap_acquire(w.map_a);
                     tensormap_acquire(w.map_blo);
                     last_group = w.group;
                 }
-                for (int i = 0; i < w.k_tile_count; ++i) {
+                for (int i = 0; i < pc.kt_count; ++i) {
                     if (!mbar_wait<true>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
                                                  kStatusProducerWait)) {
                         ok = false;
                         break;
                     }
-                    trace(1);   // stage free
-                    const uint32_t stage = smem_base + s * PairStage::kBytes;
+                    const uint32_t stage = smem_base + s * Stage::kBytes;
                     const uint32_t bar = smem_u32(&ctl->full[s]);
                     if (kTimingProbes && (flags & kFlagSkipLoads)) {   // timing probe
                         mbar_arrive(bar);
-                        if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                        if (++s == kStages) { s = 0; ph ^= 1u; }
                         continue;
                     }
-                    mbar_arrive_expect_tx(bar, PairStage::kBytes);
-                    tma_load_3d(stage + PairStage::kOffA, w.map_a, bar, i * 128, w.a_row, w.batch);
-                    tma_load_3d(stage + PairStage::kOffB, w.map_blo, bar, i * 128, w.blo_row, w.batch);
-                    const long long sf_off = static_cast<long long>(i) * kSfChunkBytes;
-                    bulk_load(stage + PairStage::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
-                    bulk_load(stage + PairStage::kOffSfB1, w.sfblo + sf_off, kSfChunkBytes, bar);
-                    bulk_load(stage + PairStage::kOffSfB2, w.sfbhi + sf_off, kSfChunkBytes, bar);
-                    if (++s == kPairStages) { s = 0; ph ^= 1u; }
+                    const int kt_index = pc.kt_begin + i;
+                    mbar_arrive_expect_tx(bar, Stage::kBytes);
+                    tma_load_3d(stage + Stage::kOffA, w.map_a, bar, kt_index * 128, w.a_row, w.batch);
+                    tma_load_3d(stage + Stage::kOffB, w.map_blo, bar, kt_index * 128, w.blo_row, w.batch);
+                    const long long sf_off = static_cast<long long>(kt_index) * kSfChunkBytes;
+                    bulk_load(stage + Stage::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
+                    bulk_load(stage + Stage::kOffSfB1, w.sfblo + sf_off, kSfChunkBytes, bar);
+                    bulk_load(stage + Stage::kOffSfB2, w.sfbhi + sf_off, kSfChunkBytes, bar);
+                    if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
             if (!ok)
@@ -433,7 +676,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         // addresses are warp-uniform values; one elected lane issues each MMA and commit.
         if (rank == 0) {
             constexpr uint32_t kUnitCols = TM::kGranule * TM::kSlotCols;
-            const uint32_t desc_lo_base = smem_desc_lo(smem_base + PairStage::kOffA);
+            const uint32_t desc_lo_base = smem_desc_lo(smem_base + Stage::kOffA);
             const uint32_t sf_ready_bar = smem_u32(&ctl->sf_ready[0]);
             const uint32_t empty_mine = smem_u32(&ctl->empty[0]);
             const uint32_t sf_base = tmem_base + TM::kSfBase;
@@ -443,8 +686,10 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
             Tracer trace(kTimingProbes && lane == 0 ? p.trace : nullptr, 0);
             const long long kernel_t0 = clock64();
             int cursor = 0;
-            for (int tile = pair; tile < total && !failed; tile += pairs, ++it) {
-                const int k_tiles = S::k_tiles(p, tile, cursor);
+            PairWalk<S> walk(p, pair, pairs);
+            PairPiece pc;
+            for (; !failed && walk.next(p, cursor, pc); ++it) {
+                const int k_tiles = pc.kt_count;
                 trace(8);
                 // the first k-tile's scale factors are normally in place long before the
                 // accumulator comes back: pass that barrier first, off the hand-back path
@@ -480,8 +725,8 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     for (int kb = 0; kb < kKBlocks; ++kb) {
                         if (kb > 0 && kb % TM::kGranule == 0) b = (b + 1 == TM::kBuffers) ? 0u : b + 1;
                         const uint32_t sfa = sf_base + b * kUnitCols + (kb % TM::kGranule) * TM::kSlotCols;
-                        tc_mma_mxf4nvf4_pair_lo_elect(acc_addr, a_lo + 2 * kb, a_lo + (PairStage::kOffB >> 4) + 2 * kb,
-                                                      idesc_mxf4nvf4(256, T::kMmaN), sfa, sfa + 4,
+                        tc_mma_mxf4nvf4_pair_lo_elect(acc_addr, a_lo + 2 * kb, a_lo + (Stage::kOffB >> 4) + 2 * kb,
+                                                      idesc_mxf4nvf4(256, S::kMmaN), sfa, sfa + 4,
                                                       (kb > 0 || i > 0) ? 1u : 0u);
                     }
                     tc_commit_pair_both_elect(empty_mine + s * 8, 3);   // both CTAs' `empty` barriers
@@ -489,8 +734,8 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     buf += kKBlocks / TM::kGranule;
                     if (buf >= static_cast<uint32_t>(TM::kBuffers)) buf -= TM::kBuffers;
                     ++s;
-                    a_lo += PairStage::kBytes >> 4;
-                    if (s == kPairStages) { s = 0; ph ^= 1u; a_lo = desc_lo_base; }
+                    a_lo += Stage::kBytes >> 4;
+                    if (s == kStages) { s = 0; ph ^= 1u; a_lo = desc_lo_base; }
                 }
                 if (failed) break;
                 tc_commit_pair_both_elect(smem_u32(&ctl->acc_full[it & 1]), 3);
@@ -504,9 +749,17 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         // ------------------------------ epilogue (each CTA its own 128 rows)
         int it = 0, cursor = 0;
         Tracer trace(kTimingProbes && lane == 0 && blockIdx.x == 0 ? p.trace : nullptr, warp == 0 ? 7 : warp);
-        for (int tile = pair; tile < total; tile += pairs, ++it) {
-            const Work w = S::get(p, tile, rank, cursor);
+        Tracer* tr = kTimingProbes ? &trace : nullptr;
+        PairWalk<S> walk(p, pair, pairs);
+        PairPiece pc;
+        for (; walk.next(p, cursor, pc); ++it) {
+            const Work w = S::get(p, pc.tile, rank, cursor);
             const uint32_t release_bar = map_to_cta(smem_u32(&ctl->acc_release[it & 1]), 0);
+            if constexpr (!TM::kOverlapped) {
+                // disjoint buffers: hand-back number `it` says "tile it - 1 is drained"
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_relaxed(release_bar);
+            }
             if (!mbar_wait<true>(smem_u32(&ctl->acc_full[it & 1]), (it >> 1) & 1, abort_flag, p.status,
                                  kStatusEpilogueWait))
                 break;
@@ -525,14 +778,40 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     epilogue_tile_grouped_pair<1>(w, tmem_base, warp, lane, release_bar, staging, store);
                 else
                     epilogue_tile_grouped_pair<0>(w, tmem_base, warp, lane, release_bar, staging, store);
-            } else {
+            } else if constexpr (S::kMmaN == 128) {
                 const int c_col = w.blo_row, c_row = w.a_row + warp * 32;
                 if (it & 1)
-                    epilogue_tile_staged<1>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store,
-                                            &trace);
+                    epilogue_tile_narrow<1>(p, w, tmem_base, warp, lane, staging, c_col, c_row, store);
                 else
-                    epilogue_tile_staged<0>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store,
-                                            &trace);
+                    epilogue_tile_narrow<0>(p, w, tmem_base, warp, lane, staging, c_col, c_row, store);
+            } else {
+                const int c_col = w.blo_row, c_row = w.a_row + warp * 32;
+                bool done = false;
+                if constexpr (S::kStreamK) {
+                    if (pc.kind == 1) {
+                        if (it & 1) epilogue_partial_store<1>(p, tmem_base, rank, warp, lane, release_bar, pair);
+                        else epilogue_partial_store<0>(p, tmem_base, rank, warp, lane, release_bar, pair);
+                        done = true;
+                    } else if (pc.kind == 2) {
+                        // partial sums of this warp's rows, published by the next pair
+                        const float* partial = p.splitk_ws + static_cast<size_t>(pair + 1) * kStreamKSlotFloats +
+                                               static_cast<size_t>(rank * 4 + warp) * (64 * 128) + lane * 4;
+                        if (!wait_partial(p, pair + 1, rank, warp, abort_flag)) break;
+                        if (it & 1)
+                            epilogue_tile_staged<1, true>(p, w, tmem_base, warp, lane, release_bar, staging, c_col,
+                                                          c_row, store, tr, partial);
+                        else
+                            epilogue_tile_staged<0, true>(p, w, tmem_base, warp, lane, release_bar, staging, c_col,
+                                                          c_row, store, tr, partial);
+                        done = true;
+                    }
+                }
+                if (done) {
+                } else if (it & 1) {
+                    epilogue_tile_staged<1>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store, tr);
+                } else {
+                    epilogue_tile_staged<0>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store, tr);
+                }
             }
             trace(2);   // tile stored
             tc_fence_before_sync();

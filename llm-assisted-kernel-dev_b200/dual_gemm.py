@@ -35,6 +35,24 @@ def _splitk_workspace(lib, device: torch.device, m: int, n: int, k: int, l: int)
     return (ws.data_ptr() + 255) & ~255, nbytes
 
 
+# Scratch of the CTA-pair kernel's stream-k tail (fp32 partial sums of the tiles that two pairs
+# share + flag words; zero-filled once): one per device and stream, because launches that overlap
+# on the GPU must not share it.
+_streamk_workspaces: dict = {}
+
+
+def _streamk_workspace(lib, device: torch.device, stream: int, m: int, n: int, k: int, l: int):
+    nbytes = int(lib.b200_dual_streamk_workspace_bytes(m, n, k, l))
+    if nbytes == 0:
+        return None, 0
+    key = (device.index, stream)
+    ws = _streamk_workspaces.get(key)
+    if ws is None or ws.numel() < nbytes + 256:
+        ws = torch.zeros(nbytes + 256, dtype=torch.uint8, device=device)
+        _streamk_workspaces[key] = ws
+    return (ws.data_ptr() + 255) & ~255, nbytes
+
+
 def _validate(a, b1, b2, sfa_perm, sfb1_perm, sfb2_perm, c, m, n, k, l) -> None:
     if c.dtype != torch.float16:
         raise ValueError(f"c must be float16, got {c.dtype}")
@@ -76,9 +94,10 @@ def dual_gemm(a, b1, b2, sfa_perm, sfb1_perm, sfb2_perm, c, *, variant: int = _l
     status       optional 1-element uint32/int32 CUDA tensor receiving a non-zero
                  code if an on-device wait times out
     """
+    stream = torch.cuda.current_stream(c.device).cuda_stream if c.is_cuda else 0
     key = (a.data_ptr(), b1.data_ptr(), b2.data_ptr(), sfa_perm.data_ptr(), sfb1_perm.data_ptr(),
            sfb2_perm.data_ptr(), c.data_ptr(), c.shape, c.stride(), a.shape[1], variant,
-           0 if status is None else status.data_ptr())
+           0 if status is None else status.data_ptr(), stream)
     plan = _plans.get(key)
     if plan is None:
         if not c.is_cuda:
@@ -91,6 +110,8 @@ def dual_gemm(a, b1, b2, sfa_perm, sfb1_perm, sfb2_perm, c, *, variant: int = _l
         ws_ptr, ws_bytes = (None, 0)
         if variant == _lib.VARIANT_SPLITK:
             ws_ptr, ws_bytes = _splitk_workspace(lib, c.device, m, n, k, l)
+        elif variant in (_lib.VARIANT_AUTO, _lib.VARIANT_PAIR_STREAMK) and m % 256 == 0:
+            ws_ptr, ws_bytes = _streamk_workspace(lib, c.device, stream, m, n, k, l)
         args = (key[0], key[1], key[2], key[3], key[4], key[5], key[6], m, n, k, l, c.stride(0),
                 c.stride(2) if l > 1 else 0, 0, 0, variant, ws_ptr, ws_bytes)
         plan = (lib.b200_dual_gemm_nvfp4_ex, args, c.device, c.device.index,
@@ -99,7 +120,7 @@ def dual_gemm(a, b1, b2, sfa_perm, sfb1_perm, sfb2_perm, c, *, variant: int = _l
             _plans.pop(next(iter(_plans)))
         _plans[key] = plan
     fn, args, device, index, status_ptr = plan
-    code = fn(*args, torch.cuda.current_stream(device).cuda_stream, index, status_ptr)
+    code = fn(*args, stream, index, status_ptr)
     if code:
         _lib.check(code)
     return c

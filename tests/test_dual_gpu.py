@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 TOL_NORTH_STAR = 1e-2
 TOL_REFERENCE = 1e-3
 
-V_AUTO, V_PERSISTENT, V_SERIAL, V_SERIAL_2MMA, V_SPLITK, V_PAIR = 0, 1, 2, 3, 4, 5
+V_AUTO, V_PERSISTENT, V_SERIAL, V_SERIAL_2MMA, V_SPLITK, V_PAIR, V_PAIR_NARROW, V_PAIR_STREAMK = 0, 1, 2, 3, 4, 5, 6, 7
 
 
 def _run(pkg, data, variant):
@@ -104,6 +104,60 @@ def test_cta_pair_variant(pkg, oracle, m, n, k, l, dist, tol):
     again = _run(pkg, data, V_PAIR)
     # same MMAs in the same k order: the pair kernel reproduces the one-CTA kernel bit for bit
     assert torch.equal(again.view(torch.int16), one_cta.view(torch.int16))
+
+
+# CTA pairs on 256 x 64 tiles (the library's choice for shapes with few tiles): one tile, both halves of a
+# scale-factor atom, several k-tiles and tiles per pair, batches, the reference task's benchmark shapes
+@pytest.mark.parametrize("m,n,k,l", [(256, 128, 256, 1), (256, 384, 2560, 1), (512, 256, 512, 2), (2048, 1024, 1536, 1),
+                                     (256, 4096, 7168, 1), (256, 3072, 4096, 1)])
+@pytest.mark.parametrize("dist,tol", [("reference", TOL_REFERENCE), ("uniform16", TOL_NORTH_STAR)])
+def test_narrow_cta_pair_variant(pkg, oracle, m, n, k, l, dist, tol):
+    data = pkg.inputs.generate_input(m, n, k, l, 13, dist=dist, device="cuda")
+    out = _run(pkg, data, V_PAIR_NARROW)
+    _check(oracle, data, out, tol)
+    one_cta = _run(pkg, data, V_PERSISTENT).clone()
+    again = _run(pkg, data, V_PAIR_NARROW)
+    # same products summed in the same k order: the same bits as the one-CTA kernel
+    assert torch.equal(again.view(torch.int16), one_cta.view(torch.int16))
+
+
+def test_library_picks_narrow_tiles_for_few_tiles(pkg):
+    for (m, n, k), want in (((256, 4096, 7168), "PairDualNarrow"), ((512, 4096, 7168), "PairDual>"),
+                            ((256, 3072, 4096), "PairDualNarrow"), ((512, 3072, 7168), "PairDual>"),
+                            ((128, 256, 512), "persistent<Dual>")):
+        data = pkg.inputs.generate_input(m, n, k, 1, 0, dist="reference", device="cuda")
+        _run(pkg, data, V_AUTO)
+        assert want in pkg._lib.last_kernel(), (m, n, k, pkg._lib.last_kernel())
+
+
+# Stream-k tail: 80 = 74 + 6 pair tiles (everything is cut), 152 = 74 + 78 (one whole round, then the cut part),
+# two k-tiles per tile (the smallest that can be cut), ten k-tiles; on a 148-SM GPU
+@pytest.mark.parametrize("m,n,k", [(1024, 2560, 1024), (2048, 2432, 512), (512, 5120, 2560), (2048, 2432, 1280)])
+@pytest.mark.parametrize("dist,tol", [("reference", TOL_REFERENCE), ("uniform16", TOL_NORTH_STAR)])
+def test_stream_k_tail(pkg, oracle, m, n, k, dist, tol):
+    data = pkg.inputs.generate_input(m, n, k, 1, 17, dist=dist, device="cuda")
+    out = _run(pkg, data, V_PAIR_STREAMK).clone()
+    assert "StreamK" in pkg._lib.last_kernel()
+    _check(oracle, data, out, tol)
+    # the cut is fixed by the shape: a second run gives the same bits; the library's own choice is this kernel too
+    again = _run(pkg, data, V_AUTO)
+    assert "StreamK" in pkg._lib.last_kernel()
+    assert torch.equal(again.view(torch.int16), out.view(torch.int16))
+    # against whole tiles only the tiles that two pairs share differ, by fp32 re-association
+    whole = _run(pkg, data, V_PAIR)
+    assert oracle.compare(out, whole, tol, tol) == []
+
+
+def test_stream_k_needs_its_workspace(pkg):
+    lib = pkg._lib.load()
+    assert lib.b200_dual_streamk_workspace_bytes(1024, 2560, 1024, 1) == 74 * (256 * 1024) + 2560
+    assert lib.b200_dual_streamk_workspace_bytes(8192, 14336 // 8, 4096, 1) > 0      # 448 tiles on 74 pairs
+    assert lib.b200_dual_streamk_workspace_bytes(256 * 74, 128, 1024, 1) == 0        # whole rounds: nothing to cut
+    d = pkg.inputs.generate_input(1024, 2560, 1024, 1, 0, device="cuda")
+    rc = lib.b200_dual_gemm_nvfp4_ex(d[0].data_ptr(), d[1].data_ptr(), d[2].data_ptr(), d[6].data_ptr(), d[7].data_ptr(),
+                                     d[8].data_ptr(), d[9].data_ptr(), 1024, 2560, 1024, 1, 2560, 0, 0, 0, V_PAIR_STREAMK,
+                                     None, 0, None, 0, None)
+    assert rc == pkg._lib.E_WORKSPACE
 
 
 def test_cta_pair_needs_even_row_tiles(pkg):

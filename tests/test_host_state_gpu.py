@@ -102,10 +102,11 @@ def test_upload_is_refused_while_the_stream_is_captured(pkg, oracle):
     data = pkg.inputs.generate_grouped_input([136, 40], [256, 128], [256, 512], 2, 33, dist="reference", device="cuda",
                                              fill_c=100.0)
     fresh = pkg.inputs.generate_grouped_input([96], [128], [256], 1, 34, dist="reference", device="cuda", fill_c=100.0)
-    gg.custom_kernel(data)                               # table uploaded, per-device set-up done
-    gg.custom_kernel_no_alloc(fresh)
-    torch.cuda.synchronize()
     stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        gg.custom_kernel(data)                           # table uploaded from the stream that will be captured
+        gg.custom_kernel_no_alloc(fresh)                 # per-device set-up of the static entry point done
+    torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
     refused = []
     with torch.cuda.stream(stream):
