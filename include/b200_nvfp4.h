@@ -35,9 +35,7 @@ extern "C" {
 /* Kernel variants (the `variant` argument of the *_ex entry points). */
 #define B200_VARIANT_AUTO 0       /* library picks by shape.  Dual GEMM with m % 256 == 0:
                                      PAIR_NARROW when all 256 x 64 tiles fit one round of
-                                     the GPU's CTA pairs, else PAIR (with a stream-k tail
-                                     when a workspace is given and whole tiles would leave
-                                     the last round under-filled); other m: PERSISTENT   */
+                                     the GPU's CTA pairs, else PAIR; other m: PERSISTENT  */
 #define B200_VARIANT_PERSISTENT 1 /* warp-specialised persistent kernel               */
 #define B200_VARIANT_SERIAL 2     /* one CTA per tile, single stage (bring-up / debug) */
 #define B200_VARIANT_SERIAL_2MMA 3/* as SERIAL but two N=128 MMAs per k-block          */
@@ -117,9 +115,9 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
 /* Bytes of scratch for the stream-k tail of the CTA-pair dual GEMM on a 148-SM B200
  * (74 pairs x 256 KiB of fp32 partial sums plus flag words), or 0 when the shape's
  * tiles fill whole rounds and nothing would be cut.  Pass it as `workspace` of
- * b200_dual_gemm_nvfp4_ex: 256-byte aligned, zero-filled once before its first use,
- * one workspace per stream.  AUTO uses it when cutting gains at least 3 %;
- * without it whole tiles are dealt round-robin. */
+ * b200_dual_gemm_nvfp4_ex with B200_VARIANT_PAIR_STREAMK: 256-byte aligned,
+ * zero-filled once before its first use, one workspace per stream.  No other
+ * variant cuts tiles. */
 size_t b200_dual_streamk_workspace_bytes(int m, int n, int k, int l);
 
 /* Bytes of split-k workspace for an (m, n, k, l) problem on a 148-SM B200;

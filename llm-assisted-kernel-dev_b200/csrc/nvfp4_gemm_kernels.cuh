@@ -306,28 +306,40 @@ template <Mode M, int kStages> constexpr uint32_t smem_bytes_persistent() {
 // ---------------------------------------------------------------------------
 // Role bodies shared by the persistent and the serial kernel
 // ---------------------------------------------------------------------------
-template <Mode M, bool kTimingProbes = false>
+// kElect: called by every lane of a converged warp with the same arguments, one elected lane
+// issues each instruction (see tma_load_3d_elect); otherwise called by one thread.
+template <Mode M, bool kTimingProbes = false, bool kElect = false>
 __device__ __forceinline__ void issue_stage_loads(const Work& w, int kt, uint32_t stage, uint32_t bar,
                                                   int flags = 0) {
     using L = StageLayout<M>;
     bool load_hi = ModeTraits<M>::kHasBHi;
     if constexpr (kTimingProbes) {
         if (flags & kFlagSkipLoads) {
-            mbar_arrive(bar);
+            if (!kElect || (threadIdx.x & 31) == 0) mbar_arrive(bar);
             return;
         }
         if (flags & kFlagSkipBHi) load_hi = false;
     }
-    mbar_arrive_expect_tx(bar, load_hi || !ModeTraits<M>::kHasBHi ? L::kTxBytes
-                                                                   : L::kTxBytes - kOperandTileBytes - kSfChunkBytes);
+    const uint32_t tx = load_hi || !ModeTraits<M>::kHasBHi ? L::kTxBytes : L::kTxBytes - kOperandTileBytes - kSfChunkBytes;
     const int kbyte = kt * 128;
-    tma_load_3d(stage + L::kOffA, w.map_a, bar, kbyte, w.a_row, w.batch);
-    tma_load_3d(stage + L::kOffBLo, w.map_blo, bar, kbyte, w.blo_row, w.batch);
-    if (load_hi) tma_load_3d(stage + L::kOffBHi, w.map_bhi, bar, kbyte, w.bhi_row, w.batch);
     const long long sf_off = static_cast<long long>(kt) * kSfChunkBytes;
-    bulk_load(stage + L::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
-    bulk_load(stage + L::kOffSfBLo, w.sfblo + sf_off, kSfChunkBytes, bar);
-    if (load_hi) bulk_load(stage + L::kOffSfBHi, w.sfbhi + sf_off, kSfChunkBytes, bar);
+    if constexpr (kElect) {
+        mbar_arrive_expect_tx_elect(bar, tx);
+        tma_load_3d_elect(stage + L::kOffA, w.map_a, bar, kbyte, w.a_row, w.batch);
+        tma_load_3d_elect(stage + L::kOffBLo, w.map_blo, bar, kbyte, w.blo_row, w.batch);
+        if (load_hi) tma_load_3d_elect(stage + L::kOffBHi, w.map_bhi, bar, kbyte, w.bhi_row, w.batch);
+        bulk_load_elect(stage + L::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
+        bulk_load_elect(stage + L::kOffSfBLo, w.sfblo + sf_off, kSfChunkBytes, bar);
+        if (load_hi) bulk_load_elect(stage + L::kOffSfBHi, w.sfbhi + sf_off, kSfChunkBytes, bar);
+    } else {
+        mbar_arrive_expect_tx(bar, tx);
+        tma_load_3d(stage + L::kOffA, w.map_a, bar, kbyte, w.a_row, w.batch);
+        tma_load_3d(stage + L::kOffBLo, w.map_blo, bar, kbyte, w.blo_row, w.batch);
+        if (load_hi) tma_load_3d(stage + L::kOffBHi, w.map_bhi, bar, kbyte, w.bhi_row, w.batch);
+        bulk_load(stage + L::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
+        bulk_load(stage + L::kOffSfBLo, w.sfblo + sf_off, kSfChunkBytes, bar);
+        if (load_hi) bulk_load(stage + L::kOffSfBHi, w.sfbhi + sf_off, kSfChunkBytes, bar);
+    }
 }
 
 // Scale factors of k-block `kb` of the k-tile in `stage`: shared memory -> TMEM slot.
@@ -823,11 +835,12 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
         }
     } else if (warp == 5) {
         // ------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp runs the loop in lock step on warp-uniform values; one elected lane issues.
+        {
             uint32_t s = 0, ph = 0;
             int cursor = 0, last_group = -1;
             bool ok = true;
-            Tracer trace(kTimingProbes ? p.trace : nullptr, 2);
+            Tracer trace(kTimingProbes && lane == 0 ? p.trace : nullptr, 2);
             for (int unit = blockIdx.x; ok && unit < total; unit += gridDim.x) {
                 const Work w = S::get(p, unit, cursor);
                 if (M != Mode::Dual && w.group != last_group) {
@@ -836,8 +849,8 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                     last_group = w.group;
                 }
                 for (int i = 0; i < w.k_tile_count; ++i) {
-                    if (!mbar_wait<true, kLimit>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
-                                         kStatusProducerWait)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait<true, kLimit>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag,
+                                                                         p.status, kStatusProducerWait))) {
                         ok = false;
                         break;
                     }
@@ -846,8 +859,8 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
                         if (++s == kStages) { s = 0; ph ^= 1u; }
                         continue;
                     }
-                    issue_stage_loads<M, kTimingProbes>(w, w.k_tile_begin + i, smem_base + s * L::kBytes,
-                                                        smem_u32(&ctl->full[s]), flags);
+                    issue_stage_loads<M, kTimingProbes, true>(w, w.k_tile_begin + i, smem_base + s * L::kBytes,
+                                                              smem_u32(&ctl->full[s]), flags);
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }

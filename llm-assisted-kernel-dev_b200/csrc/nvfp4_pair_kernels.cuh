@@ -525,6 +525,16 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
     const int pairs = gridDim.x >> 1;
     const long long launch_t0 = clock64();
 
+    if constexpr (!S::kGrouped) {
+        // the descriptors the first loads need: fetched while the CTA sets itself up
+        if (threadIdx.x == 160) {
+            int cursor0 = 0;
+            const Work w0 = S::get(p, pair, rank, cursor0);
+            prefetch_tensormap(w0.map_a);
+            prefetch_tensormap(w0.map_blo);
+            if (!S::kQuantOut) prefetch_tensormap(&p.map_c);
+        }
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
@@ -562,6 +572,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         uint32_t s = 0, ph = 0, kt = 0, buf = 0, units = 0, retired = 0, rs = 0, rph = 0;
         bool ok = true;
         int cursor = 0;
+        Tracer trace(kTimingProbes && lane == 0 && warp == 6 ? p.trace : nullptr, 5);
         PairWalk<S> walk(p, pair, pairs);
         PairPiece pc;
         while (ok && walk.next(p, cursor, pc)) {
@@ -571,6 +582,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     ok = false;
                     break;
                 }
+                trace(1);   // operands landed
                 uint32_t v[kKBlocks * kWordsPerBlock];
                 const uint32_t src = smem_base + s * Stage::kBytes + lane * 16;
                 if (!(kTimingProbes && (flags & kFlagSkipBHi)))   // timing probe (bit reused): no scale-factor reads
@@ -623,18 +635,22 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&ctl->sf_ready[s]), 0));
+                trace(3);   // handed to the MMA warp
                 ++kt;
                 if (++s == kStages) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 5) {
         // ------------------------------ TMA producer (each CTA for itself)
-        if (lane == 0) {
+        // The whole warp runs the loop in lock step on warp-uniform values; one elected lane issues.
+        {
             uint32_t s = 0, ph = 0;
             bool ok = true;
             int cursor = 0, last_group = -1;
+            Tracer trace(kTimingProbes && lane == 0 ? p.trace : nullptr, 4);
             PairWalk<S> walk(p, pair, pairs);
             PairPiece pc;
+            trace(10);   // producer starts
             while (ok && walk.next(p, cursor, pc)) {
                 const Work w = S::get(p, pc.tile, rank, cursor);
                 if (S::kGrouped && w.group != last_group) {   // tensor maps of a new group, written by the host
@@ -643,26 +659,27 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     last_group = w.group;
                 }
                 for (int i = 0; i < pc.kt_count; ++i) {
-                    if (!mbar_wait<true>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
-                                                 kStatusProducerWait)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait<true>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
+                                                                 kStatusProducerWait))) {
                         ok = false;
                         break;
                     }
                     const uint32_t stage = smem_base + s * Stage::kBytes;
                     const uint32_t bar = smem_u32(&ctl->full[s]);
                     if (kTimingProbes && (flags & kFlagSkipLoads)) {   // timing probe
-                        mbar_arrive(bar);
+                        if (lane == 0) mbar_arrive(bar);
                         if (++s == kStages) { s = 0; ph ^= 1u; }
                         continue;
                     }
                     const int kt_index = pc.kt_begin + i;
-                    mbar_arrive_expect_tx(bar, Stage::kBytes);
-                    tma_load_3d(stage + Stage::kOffA, w.map_a, bar, kt_index * 128, w.a_row, w.batch);
-                    tma_load_3d(stage + Stage::kOffB, w.map_blo, bar, kt_index * 128, w.blo_row, w.batch);
+                    mbar_arrive_expect_tx_elect(bar, Stage::kBytes);
+                    tma_load_3d_elect(stage + Stage::kOffA, w.map_a, bar, kt_index * 128, w.a_row, w.batch);
+                    tma_load_3d_elect(stage + Stage::kOffB, w.map_blo, bar, kt_index * 128, w.blo_row, w.batch);
                     const long long sf_off = static_cast<long long>(kt_index) * kSfChunkBytes;
-                    bulk_load(stage + Stage::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
-                    bulk_load(stage + Stage::kOffSfB1, w.sfblo + sf_off, kSfChunkBytes, bar);
-                    bulk_load(stage + Stage::kOffSfB2, w.sfbhi + sf_off, kSfChunkBytes, bar);
+                    bulk_load_elect(stage + Stage::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
+                    bulk_load_elect(stage + Stage::kOffSfB1, w.sfblo + sf_off, kSfChunkBytes, bar);
+                    bulk_load_elect(stage + Stage::kOffSfB2, w.sfbhi + sf_off, kSfChunkBytes, bar);
+                    trace(1);   // k-tile's loads issued
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -832,6 +849,10 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         tmem_dealloc_pair(tmem_base, kTmemColumns);
     }
     if (blockIdx.x == 0 && threadIdx.x == 0 && p.cycles) *p.cycles = static_cast<unsigned long long>(clock64() - launch_t0);
+    if (kTimingProbes && blockIdx.x == 0 && threadIdx.x == 0 && p.trace) {
+        p.trace[8 * 1024 - 2] = static_cast<unsigned long long>(launch_t0);
+        p.trace[8 * 1024 - 3] = static_cast<unsigned long long>(clock64());
+    }
 }
 
 }  // namespace b200

@@ -265,6 +265,41 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const void* map, 
         : "memory");
 }
 
+// Warp-collective forms of the producer's instructions: every lane of a converged warp executes
+// the call with the same arguments and one elected lane issues.  Inside an `if (lane == 0)`
+// branch each of these costs the issuing thread 100-150 cycles (five per k-tile made the producer
+// the slowest role: ~750 cycles per k-tile); predicated on elect.sync in warp-uniform code the
+// operands stay in uniform registers.
+__device__ __forceinline__ void mbar_arrive_expect_tx_elect(uint32_t bar, uint32_t bytes) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t"
+        "}\n" ::"r"(bar), "r"(bytes)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_elect(uint32_t smem_dst, const void* map, uint32_t bar, int c0, int c1,
+                                                  int c2) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];\n\t"
+        "}\n" ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load_elect(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred e;\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t"
+        "}\n" ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
 // Untiled bulk copy global -> shared (16-byte aligned, size multiple of 16).
 __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes,
                                           uint32_t bar) {

@@ -110,7 +110,7 @@ def dual_gemm(a, b1, b2, sfa_perm, sfb1_perm, sfb2_perm, c, *, variant: int = _l
         ws_ptr, ws_bytes = (None, 0)
         if variant == _lib.VARIANT_SPLITK:
             ws_ptr, ws_bytes = _splitk_workspace(lib, c.device, m, n, k, l)
-        elif variant in (_lib.VARIANT_AUTO, _lib.VARIANT_PAIR_STREAMK) and m % 256 == 0:
+        elif variant == _lib.VARIANT_PAIR_STREAMK and m % 256 == 0:
             ws_ptr, ws_bytes = _streamk_workspace(lib, c.device, stream, m, n, k, l)
         args = (key[0], key[1], key[2], key[3], key[4], key[5], key[6], m, n, k, l, c.stride(0),
                 c.stride(2) if l > 1 else 0, 0, 0, variant, ws_ptr, ws_bytes)
