@@ -260,12 +260,25 @@ size_t splitk_bytes(size_t tiles, int splits) {
     return splits <= 1 ? 0 : splitk_flag_bytes(tiles) + tiles * splits * 128 * 256 * sizeof(float);
 }
 
+// Both GEMM kernels are launched with the programmatic-stream-serialization attribute: they signal
+// `launch_dependents` on entry and wait for their predecessors (griddepcontrol.wait) before they touch
+// global memory, so back-to-back launches overlap one kernel's set-up with the tail of the one before.
+// `pdl` = false for a launch that directly follows a host-to-device copy it depends on.
 template <Mode M, int kStages, typename P, bool kTimingProbes = false, bool kInjectLostLoad = false>
-int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStream_t stream) {
+int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStream_t stream, bool pdl = true) {
     const int grid = units < sm_count ? units : sm_count;
-    nvfp4_gemm_persistent<M, kStages, kTimingProbes, kInjectLostLoad>
-        <<<grid, kPersistentThreads, smem_bytes_persistent<M, kStages>(), stream>>>(prob, flags);
-    B200_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kPersistentThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes_persistent<M, kStages>();
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    B200_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemm_persistent<M, kStages, kTimingProbes, kInjectLostLoad>, prob, flags));
     ++g_launches;
     g_last_kernel = M == Mode::Dual ? "nvfp4_gemm_persistent<Dual>"
                     : M == Mode::Group128 ? "nvfp4_gemm_persistent<Group128>" : "nvfp4_gemm_persistent<Group256>";
@@ -274,7 +287,8 @@ int launch_persistent(const P& prob, int units, int sm_count, int flags, cudaStr
 
 // CTA pairs: clusters of two CTAs, one pair per TPC, each pair walks pair tiles.
 template <typename S, bool kTimingProbes = false>
-int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, int flags, cudaStream_t stream) {
+int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, int flags, cudaStream_t stream,
+                bool pdl = true) {
     int pairs = sm_count / 2;
     if (pairs > pair_tiles) pairs = pair_tiles;
     cudaLaunchConfig_t cfg;
@@ -283,13 +297,15 @@ int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, in
     cfg.blockDim = dim3(320, 1, 1);
     cfg.dynamicSmemBytes = pair_smem_bytes<S>();
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl ? 2 : 1;
     B200_CUDA(cudaLaunchKernelEx(&cfg, nvfp4_gemm_pair<S, kTimingProbes>, prob, flags));
     ++g_launches;
     g_last_kernel = S::kName;
@@ -689,6 +705,7 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     if (g_workspaces.size() > 256 && !g_workspaces.count({device, workspace})) drop_workspace_images();
     WorkspaceImage& img = g_workspaces[{device, workspace}];
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool uploads = img.key != key;
     if (img.key != key) {
         if ((rc = reject_capture(s, "grouped gemm"))) return rc;
         std::vector<GroupEntry> table(groups);
@@ -721,14 +738,15 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     p.status = status ? status : st->status;
     p.cycles = st->cycles;
     p.trace = nullptr;
-    if (cur.tile_n == kTilingPair) return launch_pair<PairGrouped>(p, p.total_tiles, st->sm_count, 0, s);
+    const bool pdl = !uploads;    // the launch behind the table's copy keeps its full stream dependency
+    if (cur.tile_n == kTilingPair) return launch_pair<PairGrouped>(p, p.total_tiles, st->sm_count, 0, s, pdl);
     if (variant == B200_VARIANT_SERIAL) {
         return cur.tile_n == 256 ? launch_serial<Mode::Group256>(p, p.total_tiles, 0, s)
                                  : launch_serial<Mode::Group128>(p, p.total_tiles, 0, s);
     }
     return cur.tile_n == 256
-               ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s)
-               : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s);
+               ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s, pdl)
+               : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s, pdl);
 }
 
 int b200_grouped_gemm_nvfp4(int groups, const void* const* a, const void* const* b, const void* const* sfa,
@@ -849,8 +867,8 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
     p.status = status ? status : st->status;
     p.cycles = st->cycles;
     p.trace = nullptr;
-    return tile_n == 256 ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s)
-                         : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s);
+    return tile_n == 256 ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s, false)
+                         : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s, false);
 }
 
 size_t b200_quantize_sf_bytes(int rows, int k) {

@@ -680,6 +680,7 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const long long launch_t0 = clock64();
+    griddep_launch_dependents();   // the next launch may move onto SMs as this grid's CTAs leave them
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -707,6 +708,9 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
     const uint32_t tmem_base = ctl->tmem_base;
     const int total = S::total_units(p);
     volatile uint32_t* abort_flag = &ctl->abort_flag;
+    // Everything above touched only this CTA's own resources; from here on global memory is read and
+    // written, which must wait for the kernels before this one in the stream.
+    griddep_wait();
 
     // Register budget per warpgroup (512 threads start with 128 each): the epilogue
     // holds 128 accumulator columns in registers, everybody else needs few.

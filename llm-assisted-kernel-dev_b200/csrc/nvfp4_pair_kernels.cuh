@@ -143,7 +143,11 @@ struct PairDualNarrow {
     static constexpr bool kStreamK = false;
     static constexpr int kBRows = 64;
     static constexpr int kMmaN = 128;
+#ifdef B200_NARROW_STAGES
+    static constexpr int kStages = B200_NARROW_STAGES;
+#else
     static constexpr int kStages = 6;
+#endif
     __device__ static int total(const Params& p) { return (p.m_tiles / 2) * p.n_tiles * 2 * p.batches; }
     __device__ static int k_tiles(const Params& p, int /*tile*/, int& /*cursor*/) { return p.k_tiles; }
     __device__ static int n_blk64(const Params& p, int tile) { return (tile / (p.m_tiles / 2)) % (p.n_tiles * 2); }
@@ -524,6 +528,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
     const int pair = blockIdx.x >> 1;
     const int pairs = gridDim.x >> 1;
     const long long launch_t0 = clock64();
+    griddep_launch_dependents();   // the next launch may move onto SMs as this grid's CTAs leave them
 
     if constexpr (!S::kGrouped) {
         // the descriptors the first loads need: fetched while the CTA sets itself up
@@ -535,34 +540,46 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
             if (!S::kQuantOut) prefetch_tensormap(&p.map_c);
         }
     }
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(smem_u32(&ctl->full[s]), 1);
-            mbar_init(smem_u32(&ctl->empty[s]), 1);
-        }
+    // Barriers: one initialising thread per stage, one for the rest.
+    if (threadIdx.x < kStages) {
+        const int s = threadIdx.x;
+        mbar_init(smem_u32(&ctl->full[s]), 1);
+        mbar_init(smem_u32(&ctl->empty[s]), 1);
+        // one hand-over barrier per stage: a slot is reused only after the MMA thread
+        // passed its previous use (the stage had to be freed in between); used in CTA 0
+        mbar_init(smem_u32(&ctl->sf_ready[s]), 8);
+        fence_mbar_init();
+        fence_proxy_async_smem();
+    } else if (threadIdx.x == 32) {
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&ctl->acc_full[b]), 1);
             mbar_init(smem_u32(&ctl->acc_release[b]), 8);   // four epilogue warps in each CTA (used in CTA 0)
         }
-        // one hand-over barrier per stage: a slot is reused only after the MMA thread
-        // passed its previous use (the stage had to be freed in between); used in CTA 0
-        for (int i = 0; i < kStages; ++i) mbar_init(smem_u32(&ctl->sf_ready[i]), 8);
         mbar_init(smem_u32(&ctl->aux[0]), 1);
         ctl->abort_flag = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
     }
-    if (warp == 4) {
-        tmem_alloc_pair(smem_u32(&ctl->tmem_base), kTmemColumns);
-        tmem_relinquish_pair();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_arrive();      // the partner's barriers exist before anybody signals them
-    cluster_wait();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = ctl->tmem_base;
+    __syncthreads();       // this CTA's barriers exist
+    cluster_arrive();      // every thread arrives now; who needs the partner's barriers waits below
+    uint32_t tmem_base = 0;
     volatile uint32_t* abort_flag = &ctl->abort_flag;
+    if (warp != 5) {
+        // The producer warp needs neither tensor memory nor the partner: it starts loading while the
+        // other nine warps allocate tensor memory and meet the partner CTA.
+        if (warp == 4) {
+            tmem_alloc_pair(smem_u32(&ctl->tmem_base), kTmemColumns);
+            tmem_relinquish_pair();
+        }
+        tc_fence_before_sync();
+        consumer_bar_sync();   // the tensor-memory base address is published
+        tc_fence_after_sync();
+        tmem_base = ctl->tmem_base;
+        cluster_wait();        // the partner's barriers exist before anybody signals them
+    }
+    // Everything above touched only this CTA's own resources; from here on global memory is read and
+    // written, which must wait for the kernels before this one in the stream.
+    griddep_wait();
 
     if (warp >= 6) {
         // ------------------------------ scale factors: own shared memory -> own TMEM
@@ -687,6 +704,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 for (int i = 0; i < 64; ++i) __nanosleep(2000);   // error path: let copies in flight land
         }
         __syncwarp();
+        cluster_wait();    // completes the start-up cluster barrier this warp only arrived on
     } else if (warp == 4) {
         // ------------------------------ MMA issuer (first CTA of the pair only)
         // The whole warp runs the loop in lock step (waits included) so that descriptors and

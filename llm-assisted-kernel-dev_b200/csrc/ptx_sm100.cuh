@@ -48,6 +48,19 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ---------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
+// attribute may start while the kernel before it in the stream is still running.
+// ---------------------------------------------------------------------------
+// Let the next kernel in the stream be scheduled as soon as every CTA of this grid has said so (or
+// exited): its CTAs then start on SMs as this grid's CTAs leave them, instead of after the whole grid.
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Wait until the kernels this one depends on have completed and their writes are visible.  Returns at
+// once when the launch carried no programmatic dependency.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -592,6 +605,12 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
 // Barrier among the 128 epilogue threads only (hardware barrier 1; barrier 0 is __syncthreads).
 __device__ __forceinline__ void epilogue_bar_sync() {
     asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+// Barrier among the nine warps of the pair kernel that use tensor memory (all but the producer warp;
+// hardware barrier 2).
+__device__ __forceinline__ void consumer_bar_sync() {
+    asm volatile("bar.sync 2, 288;" ::: "memory");
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
