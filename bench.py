@@ -316,6 +316,59 @@ def run_quantize_only(args):
                       "note": "quantiser-only run for profiler captures"}), flush=True)
 
 
+def run_moe(torch, pkg, device, peaks, steps, warmup):
+    tokens, experts, top_k, n, k = 8192, 64, 8, 2048, 7168
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn((tokens, k), generator=gen).to(torch.bfloat16).to(device)
+    logits = torch.randn((tokens, experts), generator=gen).to(device)
+    wdata = pkg.inputs.generate_grouped_input([0] * experts, [n] * experts, [k] * experts, experts, 0, dist="uniform16",
+                                              device=device)
+    weights = pkg.moe.MoEWeights([abc[1] for abc in wdata[0]], [sf[1] for sf in wdata[2]])
+    lib = pkg._lib.load()
+    run = (lambda i: pkg.moe.moe_forward(x, logits, None, weights, n_group=8, topk_group=4, top_k=top_k,
+                                         routed_scaling=2.5, return_plan=True))
+    out, buf = run(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    dev = torch.cuda.current_device()
+    rows = tokens * top_k
+    steps_of = {
+        "route": lambda i: pkg.moe.route(logits, None, 8, 4, top_k, 2.5, out=(buf.topk_idx, buf.topk_w)),
+        "plan": lambda i: lib.b200_moe_plan(buf.topk_idx.data_ptr(), tokens, experts, top_k, buf.counts.data_ptr(),
+                                            buf.row_offsets.data_ptr(), buf.sfa_atom_offsets.data_ptr(),
+                                            buf.row_of.data_ptr(), buf.src_token.data_ptr(), buf.scratch.data_ptr(),
+                                            buf.scratch.numel(), stream, dev),
+        "gather_quantize": lambda i: lib.b200_moe_gather_quantize(x.data_ptr(), pkg._lib.DTYPE_BF16, tokens, k, x.stride(0),
+                                                                  buf.src_token.data_ptr(), buf.row_offsets.data_ptr(),
+                                                                  buf.sfa_atom_offsets.data_ptr(), experts, top_k,
+                                                                  buf.a_q.data_ptr(), buf.sfa.data_ptr(), stream, dev),
+        "grouped_gemm": lambda i: lib.b200_moe_grouped_gemm_nvfp4(experts, buf.a_q.data_ptr(), buf.sfa.data_ptr(), rows,
+                                                                  weights.b_ptrs, weights.sfb_ptrs, n, k,
+                                                                  buf.counts.data_ptr(), buf.row_offsets.data_ptr(),
+                                                                  buf.sfa_atom_offsets.data_ptr(), buf.y.data_ptr(),
+                                                                  buf.ws_ptr, buf.ws_bytes, stream, dev, None),
+        "combine": lambda i: lib.b200_moe_combine(buf.y.data_ptr(), n, buf.row_of.data_ptr(), buf.topk_w.data_ptr(), tokens,
+                                                  top_k, pkg._lib.DTYPE_BF16, out.data_ptr(), out.stride(0), stream, dev),
+    }
+    # algorithmic bytes of the HBM-bound steps
+    algo = {"route": tokens * experts * 4 + rows * 8,
+            "gather_quantize": rows * (k * 2 + k // 2 + k // 16),      # every row reads its token's bf16 row
+            "combine": rows * n * 2 + tokens * n * 2 + rows * 8}
+    res = {}
+    for name, fn in steps_of.items():
+        sec, _, _ = time_launches(torch, fn, steps, warmup, lambda: None)
+        us = sec / steps * 1e6
+        res[name] = {"us": us}
+        if name in algo:
+            res[name]["hbm_gbs"] = algo[name] / us / 1e3
+            res[name]["frac_hbm_peak"] = algo[name] / us / 1e3 / peaks["hbm_gbs"]
+    sec, _, _ = time_launches(torch, run, steps, warmup, lambda: None)
+    res["whole_layer_us"] = sec / steps * 1e6
+    res["grouped_gemm"]["tflops"] = 2.0 * rows * n * k / res["grouped_gemm"]["us"] / 1e6
+    res["note"] = ("gather_quantize re-reads a token's row once per chosen expert (8x): its algorithmic bytes count that; "
+                   "no step reads anything back to the host")
+    return res
+
+
 def run_extra(torch, pkg, device, peaks, steps, warmup):
     """Other benchmark configurations, one GPU: microseconds per launch."""
     extra = {}
@@ -393,6 +446,9 @@ def run_extra(torch, pkg, device, peaks, steps, warmup):
                                              "hbm_gbs": fmts.grouped_gemm_bytes(gsets[0][3]) / us / 1e3, "input_sets": n_in}
         del gsets
     extra["reference_task_benchmarks"] = task
+    # the whole MoE layer around that grouped GEMM: routing, plan, gather + quantise, GEMM, combine, each step
+    # timed on its own (8192 tokens, 64 experts in 8 groups of which 4 stay, top-8, N=2048, K=7168, bf16 in and out)
+    extra["moe_layer_t8192_e64_n2048_k7168"] = run_moe(torch, pkg, device, peaks, max(5, steps // 4), warmup)
     # MoE grouped GEMM, 64 experts, 8192 tokens top-8 (sum M = 65536), N=2048, K=7168
     counts = pkg.inputs.moe_expert_counts(8192, 64, 8, seed=0)
     data = pkg.inputs.generate_grouped_input(counts, [2048] * 64, [7168] * 64, 64, 0, dist="uniform16", device=device)

@@ -239,6 +239,76 @@ size_t b200_quantize_sf_bytes(int rows, int k);
 int b200_quantize_nvfp4(const void* x, int dtype, int rows, int k, int64_t ldx, void* q, void* sf,
                         void* stream, int device);
 
+/*
+ * Mixture-of-experts steps around the grouped GEMM: routing, permutation of the token
+ * rows into per-expert row ranges (quantising them to NVFP4 on the way), the expert
+ * GEMMs with a descriptor table finished on the device, and the weighted combination.
+ * They restate, for an NVFP4 expert GEMM, what the reference's MoE does with torch ops
+ * on FP8 data (moe/moe_fibench_ref.py:20-33): routing :106-134, token gather :144-153,
+ * expert GEMM :155-170, weighted accumulation :172-176.  Every array below is device
+ * memory unless it says "host"; nothing is read back to the host, so the five calls of a
+ * layer queue up on one stream without a synchronisation.
+ *
+ * b200_moe_route: DeepSeek-V3 "no-aux" routing of `tokens` rows of fp32 logits
+ *   [tokens, experts] (bias [experts] or NULL): s = sigmoid(logits), s_b = s + bias; the
+ *   experts form n_group equal groups scored by the sum of their two largest s_b; the
+ *   topk_group best groups stay; the top_k largest s_b among their experts are chosen
+ *   (ties: smaller index); weight = s / (sum of the chosen s + 1e-20) * routed_scaling.
+ *   topk_idx / topk_w [tokens, top_k], slots in descending order of s_b.
+ *   experts <= 256, n_group <= 32 and a divisor of experts, top_k <= 32.
+ *   n_group = topk_group = 1 is plain top-k.
+ */
+int b200_moe_route(const float* logits, const float* bias, int tokens, int experts, int n_group,
+                   int topk_group, int top_k, float routed_scaling, int32_t* topk_idx,
+                   float* topk_w, void* stream, int device);
+
+/* b200_moe_plan: stable counting sort of the tokens * top_k (token, slot) entries by
+ *   expert.  counts [experts]; row_offsets [experts + 1]: expert e owns rows
+ *   [row_offsets[e], row_offsets[e + 1]) of the permuted order, in token order;
+ *   sfa_atom_offsets [experts + 1]: 128-row scale-factor atoms before each expert (every
+ *   expert's scale factors start on an atom boundary); row_of [tokens * top_k]: row of
+ *   each entry; src_token [tokens * top_k]: token of each row.  scratch:
+ *   b200_moe_plan_scratch_bytes() bytes of device scratch. */
+size_t b200_moe_plan_scratch_bytes(int tokens, int experts, int top_k);
+int b200_moe_plan(const int32_t* topk_idx, int tokens, int experts, int top_k, int32_t* counts,
+                  int32_t* row_offsets, int32_t* sfa_atom_offsets, int32_t* row_of,
+                  int32_t* src_token, void* scratch, size_t scratch_bytes, void* stream,
+                  int device);
+
+/* b200_moe_gather_quantize: row r of the permuted order = x[src_token[r], :] (fp16 or
+ *   bf16, row pitch ldx) quantised exactly like b200_quantize_nvfp4: a_q [tokens * top_k,
+ *   k/2] packed e2m1 shared by all experts, sfa = b200_moe_sfa_bytes() bytes holding
+ *   every expert's reordered scale factors from its atom offset on (rows of an expert's
+ *   last atom past its count keep whatever the buffer held).  k % 64 == 0. */
+size_t b200_moe_sfa_bytes(int tokens, int experts, int top_k, int k);
+int b200_moe_gather_quantize(const void* x, int dtype, int tokens, int k, int64_t ldx,
+                             const int32_t* src_token, const int32_t* row_offsets,
+                             const int32_t* sfa_atom_offsets, int experts, int top_k, void* a_q,
+                             void* sfa, void* stream, int device);
+
+/* b200_moe_grouped_gemm_nvfp4: y[rows of expert e, :] = a_q[rows of e, :] . B_e^T for all
+ *   experts in one launch (fp16 y [total_rows, n]).  b / sfb: host arrays of device
+ *   pointers to each expert's [n, k/2] packed e2m1 weights and reordered scale factors.
+ *   The per-expert row counts stay on the device: the host uploads the constant part of
+ *   the descriptor table (tensor maps, weight pointers; only when its arguments change,
+ *   and never under stream capture) and a one-block kernel fills in counts, row ranges
+ *   and tile numbers before the GEMM kernel, which reads its tile count from device
+ *   memory.  workspace: b200_moe_gemm_workspace_bytes(experts) bytes, 256-byte aligned.
+ *   n % 128 == 0, k % 256 == 0, total_rows = tokens * top_k. */
+size_t b200_moe_gemm_workspace_bytes(int experts);
+int b200_moe_grouped_gemm_nvfp4(int experts, const void* a_q, const void* sfa, int total_rows,
+                                const void* const* b, const void* const* sfb, int n, int k,
+                                const int32_t* counts, const int32_t* row_offsets,
+                                const int32_t* sfa_atom_offsets, void* y, void* workspace,
+                                size_t workspace_bytes, void* stream, int device,
+                                uint32_t* status);
+
+/* b200_moe_combine: out[t, :] = sum over the token's top_k slots of topk_w * y[row_of, :],
+ *   accumulated in fp32 in slot order, stored as fp16 or bf16 (B200_DTYPE_*) with row
+ *   pitch ldo.  n % 8 == 0. */
+int b200_moe_combine(const void* y, int n, const int32_t* row_of, const float* topk_w, int tokens,
+                     int top_k, int out_dtype, void* out, int64_t ldo, void* stream, int device);
+
 /* Synchronise `stream`, copy the library-owned status word of `device` into
  * *out and clear it. */
 int b200_read_status(int device, void* stream, uint32_t* out);

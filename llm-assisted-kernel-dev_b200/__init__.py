@@ -8,6 +8,6 @@ kernels in ``libb200nvfp4.so`` (C ABI: include/b200_nvfp4.h).
     from <this package>.group_gemm import custom_kernel     # grouped GEMM
 """
 from . import _lib, formats, inputs  # noqa: F401
-from . import dual_gemm, group_gemm, quantize, shard  # noqa: F401
+from . import dual_gemm, group_gemm, moe, quantize, shard  # noqa: F401
 
-__all__ = ["dual_gemm", "group_gemm", "inputs", "formats", "shard"]
+__all__ = ["dual_gemm", "group_gemm", "moe", "inputs", "formats", "shard"]

@@ -43,6 +43,14 @@ SIGNATURES = {
     "b200_dual_gemm_nvfp4_quant": (_i, [_vp] * 8 + [_i] * 3 + [_vp, _i, _vp]),
     "b200_quantize_sf_bytes": (_sz, [_i, _i]),
     "b200_quantize_nvfp4": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp, _i]),
+    "b200_moe_route": (_i, [_vp, _vp, _i, _i, _i, _i, _i, ctypes.c_float, _vp, _vp, _vp, _i]),
+    "b200_moe_plan_scratch_bytes": (_sz, [_i, _i, _i]),
+    "b200_moe_plan": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _i]),
+    "b200_moe_sfa_bytes": (_sz, [_i, _i, _i, _i]),
+    "b200_moe_gather_quantize": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i]),
+    "b200_moe_gemm_workspace_bytes": (_sz, [_i]),
+    "b200_moe_grouped_gemm_nvfp4": (_i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _i, _vp]),
+    "b200_moe_combine": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _i64, _vp, _i]),
     "b200_read_status": (_i, [_i, _vp, _u32p]),
     "b200_read_last_cycles": (_i, [_i, _vp, ctypes.POINTER(ctypes.c_uint64)]),
     "b200_grouped_workspace_forget": (_i, [_i, _vp]),

@@ -14,6 +14,7 @@
 #include "nvfp4_gemm_kernels.cuh"
 #include "nvfp4_pair_kernels.cuh"
 #include "nvfp4_quantize.cuh"
+#include "moe_kernels.cuh"
 
 namespace b200 {
 namespace {
@@ -733,6 +734,7 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     const WorkspaceImage& cur = g_workspaces[{device, workspace}];
     GroupedProblem p;
     p.groups = static_cast<const GroupEntry*>(workspace);
+    p.total_tiles_dev = nullptr;
     p.num_groups = groups;
     p.total_tiles = cur.total_tiles;
     p.status = status ? status : st->status;
@@ -862,6 +864,7 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
                               cudaMemcpyHostToDevice, s));
     GroupedProblem p;
     p.groups = table_dev;
+    p.total_tiles_dev = nullptr;
     p.num_groups = groups;
     p.total_tiles = tile_begin;
     p.status = status ? status : st->status;
@@ -869,6 +872,260 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
     p.trace = nullptr;
     return tile_n == 256 ? launch_persistent<Mode::Group256, kG256Stages>(p, p.total_tiles, st->sm_count, 0, s, false)
                          : launch_persistent<Mode::Group128, kG128Stages>(p, p.total_tiles, st->sm_count, 0, s, false);
+}
+
+// --------------------------------------------------------------------------
+// Mixture-of-experts steps around the grouped GEMM
+// --------------------------------------------------------------------------
+static int moe_check_shape(const char* what, int tokens, int experts, int top_k) {
+    if (tokens <= 0 || experts <= 0 || top_k <= 0)
+        return fail(B200_E_SHAPE, "%s: tokens, experts and top_k must be positive (got %d %d %d)", what, tokens, experts,
+                    top_k);
+    if (experts > kMoeMaxExperts) return fail(B200_E_LIMIT, "%s: at most %d experts (got %d)", what, kMoeMaxExperts, experts);
+    if (top_k > 32 || top_k > experts) return fail(B200_E_SHAPE, "%s: top_k=%d must be <= 32 and <= experts", what, top_k);
+    if (static_cast<long long>(tokens) * top_k > 0x7fffffffLL / 2)
+        return fail(B200_E_LIMIT, "%s: tokens * top_k does not fit the 32-bit row index", what);
+    return 0;
+}
+
+int b200_moe_route(const float* logits, const float* bias, int tokens, int experts, int n_group, int topk_group,
+                   int top_k, float routed_scaling, int32_t* topk_idx, float* topk_w, void* stream, int device) {
+    int rc = moe_check_shape("moe route", tokens, experts, top_k);
+    if (rc) return rc;
+    if (!logits || !topk_idx || !topk_w) return fail(B200_E_NULL, "moe route: NULL tensor pointer");
+    if (n_group <= 0 || n_group > 32 || experts % n_group || topk_group <= 0 || topk_group > n_group)
+        return fail(B200_E_SHAPE, "moe route: n_group=%d must divide experts=%d, be <= 32 and >= topk_group=%d > 0", n_group,
+                    experts, topk_group);
+    if (top_k > topk_group * (experts / n_group))
+        return fail(B200_E_SHAPE, "moe route: top_k=%d exceeds the %d experts of the kept groups", top_k,
+                    topk_group * (experts / n_group));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    if ((rc = guard.enter(device))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    moe_route<<<(tokens + 7) / 8, 256, 0, s>>>(logits, bias, tokens, experts, n_group, topk_group, top_k, routed_scaling,
+                                                 topk_idx, topk_w);
+    B200_CUDA(cudaGetLastError());
+    ++g_launches;
+    g_last_kernel = "moe_route";
+    return 0;
+}
+
+size_t b200_moe_plan_scratch_bytes(int tokens, int experts, int top_k) {
+    if (tokens <= 0 || experts <= 0 || top_k <= 0) return 0;
+    const long long entries = static_cast<long long>(tokens) * top_k;
+    const long long blocks = (entries + kMoeChunk - 1) / kMoeChunk;
+    return static_cast<size_t>(blocks) * experts * sizeof(int);
+}
+
+int b200_moe_plan(const int32_t* topk_idx, int tokens, int experts, int top_k, int32_t* counts, int32_t* row_offsets,
+                  int32_t* sfa_atom_offsets, int32_t* row_of, int32_t* src_token, void* scratch, size_t scratch_bytes,
+                  void* stream, int device) {
+    int rc = moe_check_shape("moe plan", tokens, experts, top_k);
+    if (rc) return rc;
+    if (!topk_idx || !counts || !row_offsets || !sfa_atom_offsets || !row_of || !src_token || !scratch)
+        return fail(B200_E_NULL, "moe plan: NULL tensor pointer");
+    if (scratch_bytes < b200_moe_plan_scratch_bytes(tokens, experts, top_k))
+        return fail(B200_E_WORKSPACE, "moe plan: scratch has %zu bytes, %zu needed", scratch_bytes,
+                    b200_moe_plan_scratch_bytes(tokens, experts, top_k));
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    if ((rc = guard.enter(device))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int entries = tokens * top_k;
+    const int blocks = (entries + kMoeChunk - 1) / kMoeChunk;
+    int* block_counts = static_cast<int*>(scratch);
+    moe_count<<<blocks, kMoeChunk, 0, s>>>(topk_idx, entries, experts, block_counts);
+    moe_scan<<<1, kMoeMaxExperts, 0, s>>>(block_counts, blocks, experts, counts, row_offsets, sfa_atom_offsets);
+    moe_place<<<blocks, kMoeChunk, 0, s>>>(topk_idx, entries, experts, top_k, block_counts, row_offsets, row_of, src_token);
+    B200_CUDA(cudaGetLastError());
+    g_launches += 3;
+    g_last_kernel = "moe_place";
+    return 0;
+}
+
+size_t b200_moe_sfa_bytes(int tokens, int experts, int top_k, int k) {
+    if (tokens <= 0 || experts <= 0 || top_k <= 0 || k <= 0 || k % 64) return 0;
+    // every expert's rows are padded to whole 128-row atoms: at most one partly filled atom each
+    const long long atoms = (static_cast<long long>(tokens) * top_k + 127) / 128 + experts;
+    return static_cast<size_t>(atoms) * (k / 64) * 512;
+}
+
+int b200_moe_gather_quantize(const void* x, int dtype, int tokens, int k, int64_t ldx, const int32_t* src_token,
+                             const int32_t* row_offsets, const int32_t* sfa_atom_offsets, int experts, int top_k,
+                             void* a_q, void* sfa, void* stream, int device) {
+    int rc = moe_check_shape("moe gather", tokens, experts, top_k);
+    if (rc) return rc;
+    if (!x || !src_token || !row_offsets || !sfa_atom_offsets || !a_q || !sfa)
+        return fail(B200_E_NULL, "moe gather: NULL tensor pointer");
+    if (dtype != B200_DTYPE_F16 && dtype != B200_DTYPE_BF16)
+        return fail(B200_E_VARIANT, "moe gather: dtype %d is neither B200_DTYPE_F16 nor B200_DTYPE_BF16", dtype);
+    if (k <= 0 || k % 64) return fail(B200_E_SHAPE, "moe gather: k=%d is not a positive multiple of 64", k);
+    if (ldx < k || ldx % 8) return fail(B200_E_ALIGN, "moe gather: ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
+    if (!aligned16(x) || !aligned16(a_q) || !aligned16(sfa))
+        return fail(B200_E_ALIGN, "moe gather: every tensor pointer must be 16-byte aligned");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long items = static_cast<long long>(tokens) * top_k * ((k / 16 + 31) / 32);
+    long long blocks = (items + 7) / 8;
+    const long long cap = static_cast<long long>(st->sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    const uint16_t* src = static_cast<const uint16_t*>(x);
+    if (dtype == B200_DTYPE_F16)
+        moe_gather_quantize<kQuantDtypeF16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            src, ldx, src_token, row_offsets, sfa_atom_offsets, experts, k, static_cast<uint8_t*>(a_q),
+            static_cast<uint8_t*>(sfa));
+    else
+        moe_gather_quantize<kQuantDtypeBF16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            src, ldx, src_token, row_offsets, sfa_atom_offsets, experts, k, static_cast<uint8_t*>(a_q),
+            static_cast<uint8_t*>(sfa));
+    B200_CUDA(cudaGetLastError());
+    ++g_launches;
+    g_last_kernel = "moe_gather_quantize";
+    return 0;
+}
+
+size_t b200_moe_gemm_workspace_bytes(int experts) {
+    if (experts <= 0) return 0;
+    return static_cast<size_t>(experts) * sizeof(GroupEntry) + 256;      // table + the tile count
+}
+
+int b200_moe_grouped_gemm_nvfp4(int experts, const void* a_q, const void* sfa, int total_rows, const void* const* b,
+                                const void* const* sfb, int n, int k, const int32_t* counts, const int32_t* row_offsets,
+                                const int32_t* sfa_atom_offsets, void* y, void* workspace, size_t workspace_bytes,
+                                void* stream, int device, uint32_t* status) {
+    if (experts <= 0 || experts > kMoeMaxExperts)
+        return fail(B200_E_LIMIT, "moe gemm: experts=%d must be in 1..%d", experts, kMoeMaxExperts);
+    if (!a_q || !sfa || !b || !sfb || !counts || !row_offsets || !sfa_atom_offsets || !y)
+        return fail(B200_E_NULL, "moe gemm: NULL argument");
+    if (total_rows <= 0) return fail(B200_E_SHAPE, "moe gemm: total_rows=%d must be positive", total_rows);
+    if (n <= 0 || n % 128) return fail(B200_E_SHAPE, "moe gemm: n=%d is not a positive multiple of 128", n);
+    if (k <= 0 || k % 256) return fail(B200_E_SHAPE, "moe gemm: k=%d is not a positive multiple of 256", k);
+    if (!aligned16(a_q) || !aligned16(sfa) || !aligned16(y))
+        return fail(B200_E_ALIGN, "moe gemm: every tensor pointer must be 16-byte aligned");
+    for (int e = 0; e < experts; ++e) {
+        if (!b[e] || !sfb[e]) return fail(B200_E_NULL, "moe gemm: expert %d has a NULL weight pointer", e);
+        if (!aligned16(b[e]) || !aligned16(sfb[e]))
+            return fail(B200_E_ALIGN, "moe gemm: expert %d has a weight pointer that is not 16-byte aligned", e);
+    }
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return fail(B200_E_WORKSPACE, "moe gemm: workspace must be non-NULL and 256-byte aligned");
+    if (workspace_bytes < b200_moe_gemm_workspace_bytes(experts))
+        return fail(B200_E_WORKSPACE, "moe gemm: workspace has %zu bytes, %zu needed", workspace_bytes,
+                    b200_moe_gemm_workspace_bytes(experts));
+
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    int rc;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+    // The row counts live on the device, so the tiling is chosen from what the host knows: CTA pairs
+    // (256 x 256 tiles) when n allows it and the rows would give every pair a tile, else 128 x 128 tiles.
+    const bool use_pair = n % 256 == 0 && static_cast<long long>(total_rows / 256) * (n / 256) >= st->sm_count / 2;
+    const int tiling = use_pair ? kTilingPair : 128;
+
+    std::vector<uint8_t> key(4 * sizeof(int) + 3 * sizeof(void*) + static_cast<size_t>(experts) * 2 * sizeof(void*) + 8);
+    {
+        uint8_t* w = key.data();
+        auto put = [&w](const void* src, size_t nbytes) { memcpy(w, src, nbytes); w += nbytes; };
+        const char tag[8] = {'m', 'o', 'e', 0, 0, 0, 0, 0};
+        put(tag, 8);
+        put(&experts, sizeof(int));
+        put(&total_rows, sizeof(int));
+        put(&n, sizeof(int));
+        put(&k, sizeof(int));
+        put(&a_q, sizeof(void*));
+        put(&sfa, sizeof(void*));
+        put(&y, sizeof(void*));
+        put(b, experts * sizeof(void*));
+        put(sfb, experts * sizeof(void*));
+    }
+    if (g_workspaces.size() > 256 && !g_workspaces.count({device, workspace})) drop_workspace_images();
+    WorkspaceImage& img = g_workspaces[{device, workspace}];
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    GroupEntry* table_dev = static_cast<GroupEntry*>(workspace);
+    int* total_dev = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + static_cast<size_t>(experts) * sizeof(GroupEntry));
+    if (img.key != key) {
+        // static part of the table: one tensor map over the whole A buffer shared by all experts, one
+        // per expert's weights, shapes and B-side pointers.  The device fills in the rest every call.
+        if ((rc = reject_capture(s, "moe gemm"))) return rc;
+        std::vector<GroupEntry> table(experts);
+        memset(table.data(), 0, static_cast<size_t>(experts) * sizeof(GroupEntry));
+        CUtensorMap map_a;
+        if ((rc = encode_operand_map(&map_a, a_q, total_rows, k, 1, static_cast<long long>(total_rows) * (k / 2)))) return rc;
+        for (int e = 0; e < experts; ++e) {
+            GroupEntry& g = table[e];
+            g.map_a = map_a;
+            if ((rc = encode_operand_map(&g.map_b, b[e], n, k, 1, static_cast<long long>(n) * (k / 2)))) return rc;
+            g.sfb = static_cast<const uint8_t*>(sfb[e]);
+            g.ldc = n;
+            g.n = n;
+            g.k_tiles = k / 256;
+            g.n_tiles = use_pair ? n / 256 : n / 128;
+            g.sf_k_atoms = k / 64;
+            g.sfb_row_atoms = n / 128;
+        }
+        img.key.clear();
+        B200_CUDA(cudaMemcpyAsync(workspace, table.data(), static_cast<size_t>(experts) * sizeof(GroupEntry),
+                                  cudaMemcpyHostToDevice, s));
+        if (!img.uploaded) B200_CUDA(cudaEventCreateWithFlags(&img.uploaded, cudaEventDisableTiming));
+        B200_CUDA(cudaEventRecord(img.uploaded, s));
+        img.ordered.assign(1, s);
+        img.key = key;
+        img.tile_n = tiling;
+    } else if (std::find(img.ordered.begin(), img.ordered.end(), s) == img.ordered.end()) {
+        if ((rc = reject_capture(s, "moe gemm (first use of this workspace on the stream)"))) return rc;
+        B200_CUDA(cudaStreamWaitEvent(s, img.uploaded, 0));
+        if (img.ordered.size() >= 16) img.ordered.erase(img.ordered.begin() + 1);
+        img.ordered.push_back(s);
+    }
+    moe_fill_group_table<<<1, kMoeMaxExperts, 0, s>>>(table_dev, experts, counts, row_offsets, sfa_atom_offsets,
+                                                      static_cast<const uint8_t*>(sfa), static_cast<__half*>(y), n, k,
+                                                      use_pair ? 256 : 128, total_dev);
+    B200_CUDA(cudaGetLastError());
+    ++g_launches;
+    GroupedProblem p;
+    p.groups = table_dev;
+    p.total_tiles_dev = total_dev;
+    p.num_groups = experts;
+    p.total_tiles = 0;
+    p.status = status ? status : st->status;
+    p.cycles = st->cycles;
+    p.trace = nullptr;
+    // full grid: how many tiles there are is only known on the device
+    if (use_pair) return launch_pair<PairGrouped>(p, 1 << 30, st->sm_count, 0, s);
+    return launch_persistent<Mode::Group128, kG128Stages>(p, 1 << 30, st->sm_count, 0, s);
+}
+
+int b200_moe_combine(const void* y, int n, const int32_t* row_of, const float* topk_w, int tokens, int top_k,
+                     int out_dtype, void* out, int64_t ldo, void* stream, int device) {
+    if (!y || !row_of || !topk_w || !out) return fail(B200_E_NULL, "moe combine: NULL tensor pointer");
+    if (tokens <= 0 || top_k <= 0) return fail(B200_E_SHAPE, "moe combine: tokens and top_k must be positive");
+    if (n <= 0 || n % 8) return fail(B200_E_SHAPE, "moe combine: n=%d is not a positive multiple of 8", n);
+    if (ldo < n || ldo % 8) return fail(B200_E_ALIGN, "moe combine: ldo=%lld must be >= n and a multiple of 8", (long long)ldo);
+    if (out_dtype != B200_DTYPE_F16 && out_dtype != B200_DTYPE_BF16)
+        return fail(B200_E_VARIANT, "moe combine: out_dtype %d is neither B200_DTYPE_F16 nor B200_DTYPE_BF16", out_dtype);
+    if (!aligned16(y) || !aligned16(out)) return fail(B200_E_ALIGN, "moe combine: y and out must be 16-byte aligned");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    int rc;
+    if ((rc = guard.enter(device))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (out_dtype == B200_DTYPE_F16)
+        moe_combine<kQuantDtypeF16><<<tokens, 256, 0, s>>>(static_cast<const __half*>(y), n, row_of, topk_w, top_k,
+                                                           static_cast<uint16_t*>(out), ldo);
+    else
+        moe_combine<kQuantDtypeBF16><<<tokens, 256, 0, s>>>(static_cast<const __half*>(y), n, row_of, topk_w, top_k,
+                                                            static_cast<uint16_t*>(out), ldo);
+    B200_CUDA(cudaGetLastError());
+    ++g_launches;
+    g_last_kernel = "moe_combine";
+    return 0;
 }
 
 size_t b200_quantize_sf_bytes(int rows, int k) {

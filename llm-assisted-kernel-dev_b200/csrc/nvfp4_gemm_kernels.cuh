@@ -124,12 +124,14 @@ struct alignas(128) GroupEntry {
     long long ldc;
     int m, n, k_tiles, m_tiles;
     int n_tiles, tile_begin, sf_k_atoms, sfb_row_atoms;
-    int pad[8];
+    int a_row0;                          // first row of this group in map_a (groups that share one A buffer)
+    int pad[7];
 };
 static_assert(sizeof(GroupEntry) == 384, "GroupEntry layout");
 
 struct GroupedProblem {
     const GroupEntry* groups;
+    const int* total_tiles_dev;          // non-NULL: the tile count is read from device memory (table built on the device)
     int num_groups;
     int total_tiles;
     uint32_t* status;
@@ -197,7 +199,9 @@ template <> struct Scheduler<Mode::Dual> {
 template <Mode M> struct GroupScheduler {
     using Params = GroupedProblem;
     static constexpr int kBN = ModeTraits<M>::kOutCols;
-    __device__ static int total_units(const Params& p) { return p.total_tiles; }
+    __device__ static int total_units(const Params& p) {
+        return p.total_tiles_dev ? *p.total_tiles_dev : p.total_tiles;
+    }
     // `cursor` remembers the group of the previous (smaller) tile id so the
     // search is a short forward scan; groups with zero tiles are stepped over.
     __device__ static Work get(const Params& p, int unit, int& cursor) {
@@ -214,7 +218,7 @@ template <Mode M> struct GroupScheduler {
         Work w;
         w.map_a = &e->map_a;
         w.map_blo = w.map_bhi = &e->map_b;
-        w.a_row = m_blk * kTileM;
+        w.a_row = e->a_row0 + m_blk * kTileM;
         w.blo_row = n_blk * kBN;
         w.bhi_row = n_blk * kBN + 128;
         w.batch = 0;
@@ -706,11 +710,11 @@ nvfp4_gemm_persistent(const __grid_constant__ typename Scheduler<M>::Params p, i
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctl->tmem_base;
-    const int total = S::total_units(p);
     volatile uint32_t* abort_flag = &ctl->abort_flag;
     // Everything above touched only this CTA's own resources; from here on global memory is read and
     // written, which must wait for the kernels before this one in the stream.
     griddep_wait();
+    const int total = S::total_units(p);
 
     // Register budget per warpgroup (512 threads start with 128 each): the epilogue
     // holds 128 accumulator columns in registers, everybody else needs few.

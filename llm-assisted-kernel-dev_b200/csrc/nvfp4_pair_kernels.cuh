@@ -196,7 +196,7 @@ struct PairGrouped {
     static constexpr int kBRows = 128;
     static constexpr int kMmaN = 256;
     static constexpr int kStages = 5;
-    __device__ static int total(const Params& p) { return p.total_tiles; }
+    __device__ static int total(const Params& p) { return p.total_tiles_dev ? *p.total_tiles_dev : p.total_tiles; }
     __device__ static int sfb_half(const Params& /*p*/, int /*tile*/) { return 0; }
     __device__ static const GroupEntry* find(const Params& p, int tile, int& cursor) {
         int g = cursor;
@@ -218,7 +218,7 @@ struct PairGrouped {
         Work w;
         w.map_a = &e->map_a;
         w.map_blo = w.map_bhi = &e->map_b;
-        w.a_row = m_blk * kTileM;                          // may lie past the group's rows: TMA fills zeros
+        w.a_row = e->a_row0 + m_blk * kTileM;              // may lie past the group's rows (zeros, or another group's)
         w.blo_row = w.bhi_row = n_blk * 256 + static_cast<int>(rank) * 128;
         w.batch = 0;
         const long long sf_row = static_cast<long long>(e->sf_k_atoms) * kSfAtomBytes;
