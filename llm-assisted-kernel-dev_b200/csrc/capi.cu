@@ -295,7 +295,7 @@ int launch_pair(const typename S::Params& prob, int pair_tiles, int sm_count, in
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof cfg);
     cfg.gridDim = dim3(2 * pairs, 1, 1);
-    cfg.blockDim = dim3(320, 1, 1);
+    cfg.blockDim = dim3(kPairThreads, 1, 1);
     cfg.dynamicSmemBytes = pair_smem_bytes<S>();
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];

@@ -509,8 +509,10 @@ __device__ __forceinline__ bool wait_partial(const DenseProblem& p, int slot, ui
     return __all_sync(0xffffffffu, ok);
 }
 
+constexpr int kPairThreads = 352;   // eleven warps: 0-3 epilogue, 4 MMA, 5 operand loads, 6-9 scale factors, 10 scale-factor loads
+
 template <typename S, bool kTimingProbes = false>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(kPairThreads, 1)
 nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
     using TM = typename S::TM;
     using Stage = PairStageT<S::kBRows>;
@@ -543,7 +545,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
     // Barriers: one initialising thread per stage, one for the rest.
     if (threadIdx.x < kStages) {
         const int s = threadIdx.x;
-        mbar_init(smem_u32(&ctl->full[s]), 1);
+        mbar_init(smem_u32(&ctl->full[s]), 2);    // the two producer warps, each with its own byte count
         mbar_init(smem_u32(&ctl->empty[s]), 1);
         // one hand-over barrier per stage: a slot is reused only after the MMA thread
         // passed its previous use (the stage had to be freed in between); used in CTA 0
@@ -564,9 +566,9 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
     cluster_arrive();      // every thread arrives now; who needs the partner's barriers waits below
     uint32_t tmem_base = 0;
     volatile uint32_t* abort_flag = &ctl->abort_flag;
-    if (warp != 5) {
-        // The producer warp needs neither tensor memory nor the partner: it starts loading while the
-        // other nine warps allocate tensor memory and meet the partner CTA.
+    if (warp != 5 && warp != 10) {
+        // The two producer warps need neither tensor memory nor the partner: they start loading while
+        // the other nine warps allocate tensor memory and meet the partner CTA.
         if (warp == 4) {
             tmem_alloc_pair(smem_u32(&ctl->tmem_base), kTmemColumns);
             tmem_relinquish_pair();
@@ -581,7 +583,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
     // written, which must wait for the kernels before this one in the stream.
     griddep_wait();
 
-    if (warp >= 6) {
+    if (warp >= 6 && warp <= 9) {
         // ------------------------------ scale factors: own shared memory -> own TMEM
         const uint32_t quad_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
         constexpr uint32_t kUnitsPerKTile = kKBlocks / TM::kGranule;
@@ -657,20 +659,24 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 if (++s == kStages) { s = 0; ph ^= 1u; }
             }
         }
-    } else if (warp == 5) {
-        // ------------------------------ TMA producer (each CTA for itself)
-        // The whole warp runs the loop in lock step on warp-uniform values; one elected lane issues.
+    } else if (warp == 5 || warp == 10) {
+        // ------------------------------ TMA producers (each CTA for itself)
+        // Two warps share a k-tile's instructions, each of which costs its issuing warp 80-100 cycles:
+        // warp 5 loads the two operand tiles, warp 10 the three scale-factor chunks; each arrives on
+        // the stage's barrier (count 2) with the byte count of its own copies before it issues them.
+        // Whole warps run the loop in lock step on warp-uniform values; one elected lane issues.
         {
+            const bool operands = warp == 5;
             uint32_t s = 0, ph = 0;
             bool ok = true;
             int cursor = 0, last_group = -1;
-            Tracer trace(kTimingProbes && lane == 0 ? p.trace : nullptr, 4);
+            Tracer trace(kTimingProbes && lane == 0 && operands ? p.trace : nullptr, 4);
             PairWalk<S> walk(p, pair, pairs);
             PairPiece pc;
             trace(10);   // producer starts
             while (ok && walk.next(p, cursor, pc)) {
                 const Work w = S::get(p, pc.tile, rank, cursor);
-                if (S::kGrouped && w.group != last_group) {   // tensor maps of a new group, written by the host
+                if (S::kGrouped && operands && w.group != last_group) {   // tensor maps of a new group, written by the host
                     tensormap_acquire(w.map_a);
                     tensormap_acquire(w.map_blo);
                     last_group = w.group;
@@ -689,13 +695,17 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                         continue;
                     }
                     const int kt_index = pc.kt_begin + i;
-                    mbar_arrive_expect_tx_elect(bar, Stage::kBytes);
-                    tma_load_3d_elect(stage + Stage::kOffA, w.map_a, bar, kt_index * 128, w.a_row, w.batch);
-                    tma_load_3d_elect(stage + Stage::kOffB, w.map_blo, bar, kt_index * 128, w.blo_row, w.batch);
-                    const long long sf_off = static_cast<long long>(kt_index) * kSfChunkBytes;
-                    bulk_load_elect(stage + Stage::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
-                    bulk_load_elect(stage + Stage::kOffSfB1, w.sfblo + sf_off, kSfChunkBytes, bar);
-                    bulk_load_elect(stage + Stage::kOffSfB2, w.sfbhi + sf_off, kSfChunkBytes, bar);
+                    if (operands) {
+                        mbar_arrive_expect_tx_elect(bar, Stage::kOffSfA);              // A tile + B tile
+                        tma_load_3d_elect(stage + Stage::kOffA, w.map_a, bar, kt_index * 128, w.a_row, w.batch);
+                        tma_load_3d_elect(stage + Stage::kOffB, w.map_blo, bar, kt_index * 128, w.blo_row, w.batch);
+                    } else {
+                        const long long sf_off = static_cast<long long>(kt_index) * kSfChunkBytes;
+                        mbar_arrive_expect_tx_elect(bar, 3 * kSfChunkBytes);
+                        bulk_load_elect(stage + Stage::kOffSfA, w.sfa + sf_off, kSfChunkBytes, bar);
+                        bulk_load_elect(stage + Stage::kOffSfB1, w.sfblo + sf_off, kSfChunkBytes, bar);
+                        bulk_load_elect(stage + Stage::kOffSfB2, w.sfbhi + sf_off, kSfChunkBytes, bar);
+                    }
                     trace(1);   // k-tile's loads issued
                     if (++s == kStages) { s = 0; ph ^= 1u; }
                 }
