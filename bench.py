@@ -340,7 +340,9 @@ def run_moe(torch, pkg, device, peaks, steps, warmup):
         "gather_quantize": lambda i: lib.b200_moe_gather_quantize(x.data_ptr(), pkg._lib.DTYPE_BF16, tokens, k, x.stride(0),
                                                                   buf.src_token.data_ptr(), buf.row_offsets.data_ptr(),
                                                                   buf.sfa_atom_offsets.data_ptr(), experts, top_k,
-                                                                  buf.a_q.data_ptr(), buf.sfa.data_ptr(), stream, dev),
+                                                                  buf.a_q.data_ptr(), buf.sfa.data_ptr(),
+                                                                  buf.gather_scratch.data_ptr(), buf.gather_scratch.numel(),
+                                                                  stream, dev),
         "grouped_gemm": lambda i: lib.b200_moe_grouped_gemm_nvfp4(experts, buf.a_q.data_ptr(), buf.sfa.data_ptr(), rows,
                                                                   weights.b_ptrs, weights.sfb_ptrs, n, k,
                                                                   buf.counts.data_ptr(), buf.row_offsets.data_ptr(),
@@ -351,7 +353,9 @@ def run_moe(torch, pkg, device, peaks, steps, warmup):
     }
     # algorithmic bytes of the HBM-bound steps
     algo = {"route": tokens * experts * 4 + rows * 8,
-            "gather_quantize": rows * (k * 2 + k // 2 + k // 16),      # every row reads its token's bf16 row
+            # quantise every token once (2 B in, 9/16 B out per element), then read and write 9/16 B per element of
+            # every permuted row
+            "gather_quantize": tokens * k * 2 + tokens * (k // 2 + k // 16) + 2 * rows * (k // 2 + k // 16),
             "combine": rows * n * 2 + tokens * n * 2 + rows * 8}
     res = {}
     for name, fn in steps_of.items():
@@ -364,8 +368,8 @@ def run_moe(torch, pkg, device, peaks, steps, warmup):
     sec, _, _ = time_launches(torch, run, steps, warmup, lambda: None)
     res["whole_layer_us"] = sec / steps * 1e6
     res["grouped_gemm"]["tflops"] = 2.0 * rows * n * k / res["grouped_gemm"]["us"] / 1e6
-    res["note"] = ("gather_quantize re-reads a token's row once per chosen expert (8x): its algorithmic bytes count that; "
-                   "no step reads anything back to the host")
+    res["note"] = ("gather_quantize = one quantisation pass over the tokens + one copy of every quantised row to its "
+                   "top_k places; no step reads anything back to the host")
     return res
 
 
@@ -805,6 +809,8 @@ def main():
     ap.add_argument("--same-box", action="store_true",
                     help="one GPU: time the reference's own sm_100a kernel and the cuBLASLt NVFP4 GEMM (child process of the default run)")
     ap.add_argument("--quantize", default=None, help="ROWS,K: launch only the activation quantiser (profiler captures)")
+    ap.add_argument("--moe-layer", action="store_true",
+                    help="run only the MoE layer steps (routing, plan, gather, grouped GEMM, combine; profiler captures, one GPU)")
     ap.add_argument("--grouped", default=None, choices=["g8", "moe"],
                     help="launch only the G=8 or the 64-expert grouped GEMM (profiler captures, one GPU)")
     args = ap.parse_args()
@@ -821,6 +827,12 @@ def main():
         run_reference(args)
     elif args.same_box:
         run_same_box(args)
+    elif args.moe_layer:
+        import torch
+        torch.cuda.set_device(0)
+        pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
+        print(json.dumps({"workload": "moe_layer_t8192_e64_n2048_k7168",
+                          **run_moe(torch, pkg, "cuda:0", load_peaks(), args.steps, args.warmup)}), flush=True)
     elif args.grouped:
         run_grouped_only(args)
     elif args.quantize:

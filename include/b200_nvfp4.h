@@ -279,12 +279,16 @@ int b200_moe_plan(const int32_t* topk_idx, int tokens, int experts, int top_k, i
  *   bf16, row pitch ldx) quantised exactly like b200_quantize_nvfp4: a_q [tokens * top_k,
  *   k/2] packed e2m1 shared by all experts, sfa = b200_moe_sfa_bytes() bytes holding
  *   every expert's reordered scale factors from its atom offset on (rows of an expert's
- *   last atom past its count keep whatever the buffer held).  k % 64 == 0. */
+ *   last atom past its count keep whatever the buffer held).  Two kernels: every token
+ *   row is quantised once into `scratch` (b200_moe_gather_scratch_bytes() bytes), then
+ *   the quantised rows are copied to their top_k places.  k % 64 == 0. */
 size_t b200_moe_sfa_bytes(int tokens, int experts, int top_k, int k);
+size_t b200_moe_gather_scratch_bytes(int tokens, int k);
 int b200_moe_gather_quantize(const void* x, int dtype, int tokens, int k, int64_t ldx,
                              const int32_t* src_token, const int32_t* row_offsets,
                              const int32_t* sfa_atom_offsets, int experts, int top_k, void* a_q,
-                             void* sfa, void* stream, int device);
+                             void* sfa, void* scratch, size_t scratch_bytes, void* stream,
+                             int device);
 
 /* b200_moe_grouped_gemm_nvfp4: y[rows of expert e, :] = a_q[rows of e, :] . B_e^T for all
  *   experts in one launch (fp16 y [total_rows, n]).  b / sfb: host arrays of device

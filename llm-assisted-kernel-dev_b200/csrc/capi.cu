@@ -951,41 +951,52 @@ size_t b200_moe_sfa_bytes(int tokens, int experts, int top_k, int k) {
     return static_cast<size_t>(atoms) * (k / 64) * 512;
 }
 
+size_t b200_moe_gather_scratch_bytes(int tokens, int k) {
+    if (tokens <= 0 || k <= 0 || k % 64) return 0;
+    // packed rows, then row-major scale factors (both multiples of 16 bytes per row)
+    return static_cast<size_t>(tokens) * (k / 2) + static_cast<size_t>(tokens) * (k / 16);
+}
+
 int b200_moe_gather_quantize(const void* x, int dtype, int tokens, int k, int64_t ldx, const int32_t* src_token,
                              const int32_t* row_offsets, const int32_t* sfa_atom_offsets, int experts, int top_k,
-                             void* a_q, void* sfa, void* stream, int device) {
+                             void* a_q, void* sfa, void* scratch, size_t scratch_bytes, void* stream, int device) {
     int rc = moe_check_shape("moe gather", tokens, experts, top_k);
     if (rc) return rc;
-    if (!x || !src_token || !row_offsets || !sfa_atom_offsets || !a_q || !sfa)
+    if (!x || !src_token || !row_offsets || !sfa_atom_offsets || !a_q || !sfa || !scratch)
         return fail(B200_E_NULL, "moe gather: NULL tensor pointer");
     if (dtype != B200_DTYPE_F16 && dtype != B200_DTYPE_BF16)
         return fail(B200_E_VARIANT, "moe gather: dtype %d is neither B200_DTYPE_F16 nor B200_DTYPE_BF16", dtype);
     if (k <= 0 || k % 64) return fail(B200_E_SHAPE, "moe gather: k=%d is not a positive multiple of 64", k);
     if (ldx < k || ldx % 8) return fail(B200_E_ALIGN, "moe gather: ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
-    if (!aligned16(x) || !aligned16(a_q) || !aligned16(sfa))
+    if (!aligned16(x) || !aligned16(a_q) || !aligned16(sfa) || !aligned16(scratch))
         return fail(B200_E_ALIGN, "moe gather: every tensor pointer must be 16-byte aligned");
+    if (scratch_bytes < b200_moe_gather_scratch_bytes(tokens, k))
+        return fail(B200_E_WORKSPACE, "moe gather: scratch has %zu bytes, %zu needed", scratch_bytes,
+                    b200_moe_gather_scratch_bytes(tokens, k));
     std::lock_guard<std::mutex> lock(g_mutex);
     DeviceGuard guard;
     if ((rc = guard.enter(device))) return rc;
     DeviceState* st = nullptr;
     if ((rc = device_state(device, &st))) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const long long items = static_cast<long long>(tokens) * top_k * ((k / 16 + 31) / 32);
-    long long blocks = (items + 7) / 8;
+    uint8_t* q_rows = static_cast<uint8_t*>(scratch);
+    uint8_t* sf_rows = q_rows + static_cast<size_t>(tokens) * (k / 2);
     const long long cap = static_cast<long long>(st->sm_count) * 16;
+    long long blocks = (static_cast<long long>(tokens) * ((k / 16 + 31) / 32) + 7) / 8;
     if (blocks > cap) blocks = cap;
     const uint16_t* src = static_cast<const uint16_t*>(x);
     if (dtype == B200_DTYPE_F16)
-        moe_gather_quantize<kQuantDtypeF16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-            src, ldx, src_token, row_offsets, sfa_atom_offsets, experts, k, static_cast<uint8_t*>(a_q),
-            static_cast<uint8_t*>(sfa));
+        moe_quantize_rows<kQuantDtypeF16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(src, ldx, tokens, k, q_rows, sf_rows);
     else
-        moe_gather_quantize<kQuantDtypeBF16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
-            src, ldx, src_token, row_offsets, sfa_atom_offsets, experts, k, static_cast<uint8_t*>(a_q),
-            static_cast<uint8_t*>(sfa));
+        moe_quantize_rows<kQuantDtypeBF16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(src, ldx, tokens, k, q_rows, sf_rows);
+    blocks = (static_cast<long long>(tokens) * top_k + 7) / 8;
+    if (blocks > cap) blocks = cap;
+    moe_gather_rows<<<static_cast<unsigned>(blocks), 256, 0, s>>>(q_rows, sf_rows, src_token, row_offsets, sfa_atom_offsets,
+                                                                  experts, k, static_cast<uint8_t*>(a_q),
+                                                                  static_cast<uint8_t*>(sfa));
     B200_CUDA(cudaGetLastError());
-    ++g_launches;
-    g_last_kernel = "moe_gather_quantize";
+    g_launches += 2;
+    g_last_kernel = "moe_gather_rows";
     return 0;
 }
 

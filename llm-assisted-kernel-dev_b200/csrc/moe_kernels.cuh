@@ -8,7 +8,7 @@
 //   moe_count/scan/place  counting sort of the T * top_k (token, slot) entries by expert,
 //                         stable in token order: per-expert counts, row ranges, row of
 //                         every entry, source token of every row
-//   moe_gather_quantize   x[token] -> NVFP4 row of the expert's A operand + scale factors
+//   moe_quantize_rows / moe_gather_rows   x[token] -> NVFP4 row of the expert's A operand + scale factors
 //   moe_fill_group_table  the dynamic fields of the grouped GEMM's descriptor table
 //   moe_combine           out[t] = sum over slots of weight * y[row(t, slot)]
 // All are HBM-bound integer / byte kernels except the last two steps' arithmetic; nothing
@@ -218,26 +218,49 @@ __global__ void __launch_bounds__(kMoeMaxExperts) moe_fill_group_table(GroupEntr
     }
 }
 
-// Row r of the permuted order = activation row src_token[r], quantised like nvfp4_quantize does
-// (same block arithmetic), written as row r of the shared A buffer; its scale factors go to its
-// expert's atoms.  One lane owns one 16-element block, a warp a 512-k stretch of one row.
+// Step 1 of the gather: every token row is quantised once, like nvfp4_quantize does (same block
+// arithmetic), into a scratch copy: packed e2m1 [tokens, k/2] and its scale factors ROW-MAJOR
+// [tokens, k/16], so that a row's scale factors are contiguous for step 2.  One lane owns one
+// 16-element block, a warp a 512-k stretch of one row.
 template <int kDtype>
-__global__ void __launch_bounds__(256) moe_gather_quantize(const uint16_t* __restrict__ x, long long ldx,
-                                                           const int* __restrict__ src_token,
-                                                           const int* __restrict__ row_offsets,
-                                                           const int* __restrict__ sfa_atom_offsets, int experts,
-                                                           int k, uint8_t* __restrict__ a_q, uint8_t* __restrict__ sfa_all) {
+__global__ void __launch_bounds__(256) moe_quantize_rows(const uint16_t* __restrict__ x, long long ldx, int tokens, int k,
+                                                         uint8_t* __restrict__ q, uint8_t* __restrict__ sf_rows) {
     const int lane = threadIdx.x & 31;
-    const int total_rows = row_offsets[experts];
     const int blocks_per_row = k / 16;
     const int chunks_per_row = (blocks_per_row + 31) / 32;
-    const int rest_k = k / 64;
     const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-    const long long items = static_cast<long long>(total_rows) * chunks_per_row;
+    const long long items = static_cast<long long>(tokens) * chunks_per_row;
     for (long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); item < items;
          item += warps) {
         const int row = static_cast<int>(item / chunks_per_row);
         const int kb = static_cast<int>(item % chunks_per_row) * 32 + lane;       // 16-k block of this lane
+        if (kb < blocks_per_row) {
+            const uint16_t* src = x + static_cast<long long>(row) * ldx + kb * 16;
+            const uint4 a = __ldg(reinterpret_cast<const uint4*>(src));
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+            uint2 packed;
+            const uint32_t sbyte = quantize_block<kDtype>(a, b, packed);
+            *reinterpret_cast<uint2*>(q + static_cast<long long>(row) * (k / 2) + kb * 8) = packed;
+            sf_rows[static_cast<long long>(row) * blocks_per_row + kb] = static_cast<uint8_t>(sbyte);
+        }
+    }
+}
+
+// Step 2: row r of the permuted order = quantised row src_token[r] (quantisation is per row, so
+// this equals quantising the gathered rows).  One warp per row copies its k/2 packed bytes in
+// 16-byte pieces and scatters its k/16 scale bytes, four at a time, into its expert's atoms.  The
+// quantised activations (tokens * k * 9/16 bytes) stay in the L2 while every row is read top_k times.
+__global__ void __launch_bounds__(256) moe_gather_rows(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf_rows,
+                                                       const int* __restrict__ src_token,
+                                                       const int* __restrict__ row_offsets,
+                                                       const int* __restrict__ sfa_atom_offsets, int experts, int k,
+                                                       uint8_t* __restrict__ a_q, uint8_t* __restrict__ sfa_all) {
+    const int lane = threadIdx.x & 31;
+    const int total_rows = row_offsets[experts];
+    const int row_bytes = k / 2, sf_words = k / 64, rest_k = k / 64;
+    const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+    for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < total_rows;
+         row += warps) {
         // expert of the row: last e with row_offsets[e] <= row
         int lo = 0, hi = experts;
         while (hi - lo > 1) {
@@ -245,26 +268,16 @@ __global__ void __launch_bounds__(256) moe_gather_quantize(const uint16_t* __res
             if (row_offsets[mid] <= row) lo = mid;
             else hi = mid;
         }
-        const int local = row - row_offsets[lo];
-        const bool real = kb < blocks_per_row;
-        uint32_t sbyte = 0;
-        if (real) {
-            const uint16_t* src = x + static_cast<long long>(src_token[row]) * ldx + kb * 16;
-            const uint4 a = __ldg(reinterpret_cast<const uint4*>(src));
-            const uint4 b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
-            uint2 packed;
-            sbyte = quantize_block<kDtype>(a, b, packed);
-            *reinterpret_cast<uint2*>(a_q + static_cast<long long>(row) * (k / 2) + kb * 8) = packed;
-        }
-        uint32_t word = sbyte;
-        word |= __shfl_down_sync(0xffffffffu, sbyte, 1) << 8;
-        word |= __shfl_down_sync(0xffffffffu, sbyte, 2) << 16;
-        word |= __shfl_down_sync(0xffffffffu, sbyte, 3) << 24;
-        if (real && (lane & 3) == 0) {
-            const long long off = (static_cast<long long>(sfa_atom_offsets[lo] + local / 128) * rest_k + kb / 4) * 512 +
-                                  (local % 32) * 16 + ((local % 128) / 32) * 4;
-            *reinterpret_cast<uint32_t*>(sfa_all + off) = word;
-        }
+        const int local = static_cast<int>(row) - row_offsets[lo];
+        const long long token = src_token[row];
+        const uint4* src = reinterpret_cast<const uint4*>(q + token * row_bytes);
+        uint4* dst = reinterpret_cast<uint4*>(a_q + row * row_bytes);
+        for (int i = lane; i < row_bytes / 16; i += 32) dst[i] = __ldg(src + i);
+        const uint32_t* sf_src = reinterpret_cast<const uint32_t*>(sf_rows + token * (k / 16));
+        uint8_t* sf_dst = sfa_all + (static_cast<long long>(sfa_atom_offsets[lo] + local / 128) * rest_k) * 512 +
+                          (local % 32) * 16 + ((local % 128) / 32) * 4;
+        for (int j = lane; j < sf_words; j += 32)     // word j = the four scale factors of 64-k block j
+            *reinterpret_cast<uint32_t*>(sf_dst + static_cast<long long>(j) * 512) = __ldg(sf_src + j);
     }
 }
 

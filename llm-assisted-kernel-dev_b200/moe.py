@@ -60,6 +60,8 @@ class _Buffers:
         self.src_token = torch.empty(rows, **i32)
         self.scratch = torch.empty(max(1, int(lib.b200_moe_plan_scratch_bytes(tokens, experts, top_k))),
                                    dtype=torch.uint8, device=dev)
+        self.gather_scratch = torch.empty(max(16, int(lib.b200_moe_gather_scratch_bytes(tokens, k))), dtype=torch.uint8,
+                                          device=dev)
         self.a_q = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
         self.sfa = torch.zeros(int(lib.b200_moe_sfa_bytes(tokens, experts, top_k, k)), dtype=torch.uint8, device=dev)
         self.y = torch.empty((rows, n), dtype=torch.float16, device=dev)
@@ -132,7 +134,8 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, bias, weights: MoEWeights
                                  buf.src_token.data_ptr(), buf.scratch.data_ptr(), buf.scratch.numel(), stream, dev.index))
     _lib.check(lib.b200_moe_gather_quantize(x.data_ptr(), _dtype_code(x), tokens, k, x.stride(0), buf.src_token.data_ptr(),
                                             buf.row_offsets.data_ptr(), buf.sfa_atom_offsets.data_ptr(), experts, top_k,
-                                            buf.a_q.data_ptr(), buf.sfa.data_ptr(), stream, dev.index))
+                                            buf.a_q.data_ptr(), buf.sfa.data_ptr(), buf.gather_scratch.data_ptr(),
+                                            buf.gather_scratch.numel(), stream, dev.index))
     _lib.check(lib.b200_moe_grouped_gemm_nvfp4(experts, buf.a_q.data_ptr(), buf.sfa.data_ptr(), tokens * top_k,
                                                weights.b_ptrs, weights.sfb_ptrs, n, k, buf.counts.data_ptr(),
                                                buf.row_offsets.data_ptr(), buf.sfa_atom_offsets.data_ptr(),
