@@ -789,11 +789,11 @@ def same_box_child():
 # TFLOP/s of an MMA-only loop on all SMs with random operand bytes (instrumented build, this pool)
 MMA_ONLY_TFLOPS = 8140.0
 
-# DRAM bytes (read + write) of one full-size dual-GEMM launch: dram__bytes_read.sum 85.6 MB +
-# dram__bytes_write.sum 194.6 MB from a one-pass ncu capture of `bench.py --kernel-only`
+# DRAM bytes (read + write) of one full-size dual-GEMM launch: dram__bytes_read.sum 85.4 MB +
+# dram__bytes_write.sum 191.9 MB from a one-pass ncu capture of `bench.py --kernel-only`
 # (summary under profiles/).  Reads are the operands once;
 # part of C is still in the L2 when the launch ends.
-TRAFFIC_BYTES_PER_LAUNCH = 280.2e6
+TRAFFIC_BYTES_PER_LAUNCH = 277.3e6
 
 
 def main():

@@ -138,10 +138,16 @@ __global__ void __launch_bounds__(kMoeMaxExperts) moe_scan(int* __restrict__ blo
     const int e = threadIdx.x;
     if (e < experts) {
         int run = 0;
-        for (int b = 0; b < blocks; ++b) {
-            const int c = block_counts[b * experts + e];
-            block_counts[b * experts + e] = run;       // becomes the block's base inside the expert
-            run += c;
+        // sixteen independent loads per trip: one dependent load per block made this kernel 20 us long
+        for (int b0 = 0; b0 < blocks; b0 += 16) {
+            int c[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) c[i] = (b0 + i < blocks) ? block_counts[(b0 + i) * experts + e] : 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if (b0 + i < blocks) block_counts[(b0 + i) * experts + e] = run;   // the block's base inside the expert
+                run += c[i];
+            }
         }
         total[e] = run;
         counts[e] = run;
