@@ -647,7 +647,7 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     if (tile_n != 0 && tile_n != 128 && tile_n != 256)
         return fail(B200_E_VARIANT, "grouped gemm: tile_n=%d must be 0, 128 or 256", tile_n);
     bool all_n256 = true;
-    long long tiles128 = 0, pair_tiles = 0;
+    long long tiles128 = 0, tiles256 = 0, pair_tiles = 0;
     for (int g = 0; g < groups; ++g) {
         const int m = mnk[3 * g], n = mnk[3 * g + 1], k = mnk[3 * g + 2];
         if (m < 0 || n <= 0 || k <= 0)
@@ -661,6 +661,7 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
             return fail(B200_E_ALIGN, "grouped gemm: group %d has a pointer that is not 16-byte aligned", g);
         if (n % 256) all_n256 = false;
         tiles128 += static_cast<long long>((m + 127) / 128) * (n / 128);
+        tiles256 += static_cast<long long>((m + 127) / 128) * ((n + 255) / 256);
         pair_tiles += static_cast<long long>((m + 255) / 256) * (n / 256);
     }
     if (variant == B200_VARIANT_PAIR && !all_n256)
@@ -680,14 +681,20 @@ int b200_grouped_gemm_nvfp4_ex(int groups, const void* const* a, const void* con
     DeviceState* st = nullptr;
     if ((rc = device_state(device, &st))) return rc;
 
-    // Wide tiles halve the A traffic per flop; keep 128-wide tiles when they are
-    // needed to give every SM work or when some n is not a multiple of 256.
+    // The library's choice: the tiling with the fewest rounds x cycles per k-tile.  Measured k-tile
+    // cadences on a B200: 128 x 128 tiles ~750 cycles, 128 x 256 tiles ~1000, 256 x 256 pair tiles ~700
+    // (all k-tiles of a list are equally long in the shapes this path serves, so rounds stand for time).
     const bool tile_n_chosen_here = tile_n == 0;
-    if (tile_n == 0) tile_n = (all_n256 && tiles128 / 2 >= 2LL * st->sm_count) ? 256 : 128;
-    // CTA pairs (256 x 256 tiles): on request, or by default when every n allows it and
-    // each pair of SMs gets at least two tiles
-    const bool use_pair = variant == B200_VARIANT_PAIR ||
-                          (variant == B200_VARIANT_AUTO && tile_n_chosen_here && all_n256 && pair_tiles >= st->sm_count);
+    bool use_pair = variant == B200_VARIANT_PAIR;
+    if (tile_n == 0) {
+        const long long sms = st->sm_count, pairs = st->sm_count / 2;
+        const long long cost128 = (tiles128 + sms - 1) / sms * 750;
+        const long long cost256 = all_n256 ? (tiles256 + sms - 1) / sms * 1000 : (1LL << 60);
+        const long long cost_pair = all_n256 && variant == B200_VARIANT_AUTO ? (pair_tiles + pairs - 1) / pairs * 700 : (1LL << 60);
+        tile_n = cost256 < cost128 ? 256 : 128;
+        if (cost_pair <= cost128 && cost_pair <= cost256) use_pair = true;
+    }
+    (void)tile_n_chosen_here;
     if (use_pair) tile_n = kTilingPair;   // marks the pair tiling in the cache key and the table
 
     std::vector<uint8_t> key(sizeof(int) * 2 + groups * (5 * sizeof(void*) + 3 * sizeof(int)));
