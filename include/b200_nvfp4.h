@@ -43,7 +43,10 @@ extern "C" {
                                      fp32 partial-sum exchange before the epilogue     */
 #define B200_VARIANT_PAIR 5       /* CTA pairs (2-SM MMA, 256-row tiles).  Dual GEMM:
                                      needs m % 256 == 0.  Grouped GEMM: 256 x 256 tiles,
-                                     needs every n % 256 == 0, any m                    */
+                                     needs every n % 256 == 0, any m.  AUTO picks, for a
+                                     grouped list, the tiling (128 x 128, 128 x 256 or
+                                     pairs) with the fewest rounds x measured cycles per
+                                     k-tile                                             */
 
 #define B200_VARIANT_PAIR_NARROW 6 /* dual GEMM: CTA pairs on 256 x 64 output tiles (2-SM MMA
                                      256 x 128 x 64); for shapes with few tiles            */

@@ -618,6 +618,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                         ld_shared_v2(src + Stage::kOffSfB2 + kb * kSfAtomBytes + half_off, d[6], d[7]);
                     }
                 }
+                trace(4);   // scale factors in registers
                 // ring units of this k-tile were last read by k-tile (units + 1 - kBuffers) / kUnitsPerKTile
                 const uint32_t last_unit = units + kUnitsPerKTile - 1;
                 const bool probe_skip = kTimingProbes && (flags & kFlagSkipSfCopy) && kt >= 2;   // timing probe
@@ -636,6 +637,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                         tc_fence_after_sync();
                     }
                 }
+                trace(5);   // ring units free
                 if (!probe_skip) {
 #pragma unroll
                     for (int gr = 0; gr < static_cast<int>(kUnitsPerKTile); ++gr) {
@@ -646,7 +648,9 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                         if constexpr (kUnitWords == 24) tc_st_x8(dst + 16, v + gr * kUnitWords + 16);
                         else tc_st_x16(dst + 16, v + gr * kUnitWords + 16);
                     }
+                    trace(6);   // stores issued
                     tc_wait_st();
+                    trace(7);   // stores complete
                 }
                 units += kUnitsPerKTile;
                 buf += kUnitsPerKTile;
