@@ -479,6 +479,10 @@ def run_ours(args):
     device = f"cuda:{local}"
     pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
     pkg._lib.load()
+    if world > 1:
+        # the launcher exports OMP_NUM_THREADS=1; generating the synthetic inputs on the host may use this rank's
+        # share of the cores
+        torch.set_num_threads(max(1, (os.cpu_count() or world) // world))
     dist = None
     if world > 1:
         import torch.distributed as dist
