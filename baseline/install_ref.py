@@ -7,6 +7,7 @@ the working tree, where the reference checkout itself does not exist).
 Files taken, unmodified:
   dual_gemm/reference.py              generate_input, ref_kernel, check_implementation
   dual_gemm/submission.py             the reference's own sm_100a kernel (one CTA per tile)
+  group_gemm/group_gemm_cute4.py      the reference's grouped kernel with compile-time group dispatch
   utils/dual_gemm/{task.py,utils.py,task.yml}      task types, comparison rule, test / benchmark specs
   utils/group_gemm/{task.py,utils.py,task.yml}     the same for the grouped problem
 The reference's other kernels (dual_gemm/dual_gemm_opt_cute.py, group_gemm/group_gemm_cute5*.py)
@@ -24,6 +25,7 @@ DEST = os.path.join(HERE, "_ref")
 FILES = [
     "dual_gemm/reference.py",
     "dual_gemm/submission.py",
+    "group_gemm/group_gemm_cute4.py",
     "utils/dual_gemm/task.py",
     "utils/dual_gemm/utils.py",
     "utils/dual_gemm/task.yml",

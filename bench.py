@@ -221,6 +221,33 @@ def run_same_box(args):
     except Exception as exc:  # noqa: BLE001 - any import, JIT or launch failure is reported, not retried
         out["reference_submission_kernel"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
     try:
+        # (c) the reference's grouped kernel with compile-time group dispatch, custom_kernel of
+        # group_gemm/group_gemm_cute4.py:1252-1399, on the task's first benchmark list
+        if not ref_loader.available():
+            raise RuntimeError("baseline/_ref is not installed")
+        k4 = ref_loader.load_grouped_kernel()
+        gm, gn, gk = [80, 176, 128, 72, 64, 248, 96, 160], 4096, 7168
+        g = len(gm)
+        n_in = 3
+        gsets = [pkg.inputs.generate_grouped_input(gm, [gn] * g, [gk] * g, g, 1111 + 42 * i, dist="reference",
+                                                   device="cuda:0") for i in range(n_in)]
+        ref_out = [c.clone() for c in k4.custom_kernel(gsets[0])]
+        torch.cuda.synchronize()
+        ours_out = pkg.group_gemm.custom_kernel(gsets[0])
+        torch.cuda.synchronize()
+        same = all(bool(torch.equal(a_, b_)) for a_, b_ in zip(ref_out, ours_out))
+        for j in range(1, n_in):
+            k4.custom_kernel(gsets[j])          # the reference compiles once per list and caches per pointer set
+        torch.cuda.synchronize()
+        us_ref = timed(lambda j: k4.custom_kernel(gsets[j]), n_in)
+        us_ours = timed(lambda j: pkg.group_gemm.custom_kernel(gsets[j]), n_in)
+        out["reference_grouped_kernel_cute4"] = {"list": "G=8, M 64..248, N=4096, K=7168 (utils/group_gemm/task.yml:59)",
+                                                 "reference_kernel_us": us_ref, "this_library_us": us_ours,
+                                                 "speedup": us_ref / us_ours, "bit_identical_outputs": same,
+                                                 "input_sets": n_in}
+    except Exception as exc:  # noqa: BLE001
+        out["reference_grouped_kernel_cute4"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    try:
         from oracle import nvfp4_oracle as orc
         m, n, k = M, N, K
         data = pkg.inputs.generate_input(m, n, k, 1, 0, dist="uniform16", device="cuda:0")
