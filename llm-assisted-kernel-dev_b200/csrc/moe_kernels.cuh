@@ -123,7 +123,10 @@ __global__ void __launch_bounds__(kMoeChunk) moe_count(const int* __restrict__ t
     for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
     __syncthreads();
     const int i = blockIdx.x * kMoeChunk + threadIdx.x;
-    if (i < entries) atomicAdd(&hist[topk_idx[i]], 1);
+    if (i < entries) {
+        const int e = topk_idx[i];
+        if (static_cast<unsigned>(e) < static_cast<unsigned>(experts)) atomicAdd(&hist[e], 1);   // ids out of range are dropped
+    }
     __syncthreads();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) block_counts[blockIdx.x * experts + e] = hist[e];
 }
@@ -178,8 +181,9 @@ __global__ void __launch_bounds__(kMoeChunk) moe_place(const int* __restrict__ t
     for (int j = threadIdx.x; j < (kMoeChunk / 32) * kMoeMaxExperts; j += blockDim.x) (&warp_cnt[0][0])[j] = 0;
     __syncthreads();
     const int i = blockIdx.x * kMoeChunk + threadIdx.x;
-    const bool live = i < entries;
-    const int e = live ? topk_idx[i] : -1 - lane;              // dead lanes match nobody
+    int e = i < entries ? topk_idx[i] : -1;
+    const bool live = static_cast<unsigned>(e) < static_cast<unsigned>(experts);   // ids out of range get no row
+    if (!live) e = -1 - lane;                                   // dead lanes match nobody
     const uint32_t same = __match_any_sync(0xffffffffu, e);
     const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
     if (live && rank_in_warp == 0) warp_cnt[wib][e] = __popc(same);
