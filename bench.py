@@ -687,11 +687,12 @@ def run_ours(args):
                        "parallelism": f"64 experts (one seed-0 list) sharded by group x{world}, no collective"}
         del gdata
 
-    gather_ms = gather_ok = None
+    gather_ms = gather_ok = fused_gather = None
     if dist is not None:
         # after the metric: full C on every rank (one NCCL all-gather of the column shards); the gathered
         # matrix is checked against this rank's own shard
-        shard_c = bufs[0]["c"].permute(1, 2, 0)
+        pkg.dual_gemm.custom_kernel(dev_sets[0])
+        shard_c = dev_sets[0][9]
         for _ in range(2):
             pkg.shard.gather_dual_output(shard_c, N)
         torch.cuda.synchronize()
@@ -710,6 +711,32 @@ def run_ours(args):
         ok = torch.tensor([1.0 if same else 0.0], dtype=torch.float64, device=device)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN)
         gather_ok = bool(ok.item() == 1.0)
+        # the same result from ONE kernel per rank: the GEMM's epilogue stores every tile into the full C of
+        # every rank through peer-mapped symmetric memory (plain TMA stores over NVLink, no multicast, no NCCL)
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            c_sym = symm_mem.empty((M, N), dtype=torch.float16, device=torch.device(device))
+            hdl = symm_mem.rendezvous(c_sym, dist.group.WORLD)
+            ptrs = [int(x) for x in hdl.buffer_ptrs]
+            c_sym.fill_(float("nan"))
+            torch.cuda.synchronize()
+            barrier()
+            pkg.shard.dual_gemm_gathered(dev_sets[0], ptrs, rank, world, N)
+            torch.cuda.synchronize()
+            barrier()
+            same = bool(torch.equal(c_sym.view(torch.int16), full_c[:, :, 0].view(torch.int16)))
+            fsec, _, _ = time_launches(torch, lambda i: pkg.shard.dual_gemm_gathered(dev_sets[i % n_sets], ptrs, rank, world, N),
+                                       args.steps, 3, barrier)
+            tf = torch.tensor([fsec, 1.0 if same else 0.0], dtype=torch.float64, device=device)
+            tmax = tf.clone()
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tf, op=dist.ReduceOp.MIN)
+            fused_gather = {"ms_per_step": float(tmax[0].item()) / args.steps * 1e3, "matches_all_gather": bool(tf[1].item() == 1.0),
+                            "kernel": pkg._lib.last_kernel(), "bytes_over_nvlink_per_rank": int(2 * M * n_local * (world - 1)),
+                            "note": "GEMM + all-gather in one kernel per rank; compare with ms_per_step + c_all_gather_ms"}
+            del c_sym
+        except Exception as exc:  # noqa: BLE001 - symmetric memory may be unavailable; the NCCL path above stands
+            fused_gather = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
         del full_c
 
     # a block of launches at least a second long: the power-capped regime a serving loop sees
@@ -781,6 +808,7 @@ def run_ours(args):
     if gather_ms is not None:
         line["c_all_gather_ms"] = gather_ms
         line["c_all_gather_matches_shards"] = gather_ok
+        line["c_gather_fused_in_epilogue"] = fused_gather
     if moe_sharded is not None:
         extra["grouped_moe_g64_n2048_k7168_sharded"] = moe_sharded
     if sustained_block is not None:

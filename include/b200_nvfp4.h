@@ -115,6 +115,24 @@ int b200_dual_gemm_nvfp4_ex(const void* a, const void* b1, const void* b2, const
                             int64_t sfb_batch_bytes, int variant, void* workspace,
                             size_t workspace_bytes, void* stream, int device, uint32_t* status);
 
+/*
+ * Column shard of the dual GEMM fused with the all-gather of the shards: rank `rank`
+ * of `world` GPUs of one node computes columns [col_offset, col_offset + n_local) of
+ * C [m, n_total] and its epilogue stores every tile into the full C of EVERY rank:
+ * c_ranks[r] is rank r's [m, n_total] fp16 buffer as seen from this GPU (its own
+ * buffer for r == rank, peer-mapped addresses for the others: CUDA peer access or
+ * symmetric memory), written with plain TMA stores over NVLink, no multicast.  When
+ * all ranks' launches have completed (synchronise, then a barrier), every rank holds
+ * the whole C.  The reference is single-GPU and has no counterpart; it stands in
+ * for "shard, then all-gather" (b200_dual_gemm_nvfp4 on a shard + a collective).
+ *   a, sfa replicated; b1, b2, sfb1, sfb2 this rank's n_local rows; m % 256 == 0,
+ *   n_local, n_total, col_offset % 128 == 0, k % 256 == 0, world <= 8.
+ */
+int b200_dual_gemm_nvfp4_gather(const void* a, const void* b1, const void* b2, const void* sfa,
+                                const void* sfb1, const void* sfb2, void* const* c_ranks, int world,
+                                int rank, int m, int n_local, int n_total, int col_offset, int k,
+                                void* stream, int device, uint32_t* status);
+
 /* Bytes of scratch for the stream-k tail of the CTA-pair dual GEMM on a 148-SM B200
  * (74 pairs x 256 KiB of fp32 partial sums plus flag words), or 0 when the shape's
  * tiles fill whole rounds and nothing would be cut.  Pass it as `workspace` of

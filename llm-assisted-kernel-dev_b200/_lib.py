@@ -34,6 +34,7 @@ SIGNATURES = {
     "b200_last_kernel": (ctypes.c_char_p, []),
     "b200_dual_gemm_nvfp4": (_i, [_vp] * 7 + [_i] * 4 + [_i64, _vp, _i, _vp]),
     "b200_dual_gemm_nvfp4_ex": (_i, [_vp] * 7 + [_i] * 4 + [_i64] * 4 + [_i, _vp, _sz, _vp, _i, _vp]),
+    "b200_dual_gemm_nvfp4_gather": (_i, [_vp] * 7 + [_i] * 7 + [_vp, _i, _vp]),
     "b200_dual_splitk_workspace_bytes": (_sz, [_i] * 4),
     "b200_dual_streamk_workspace_bytes": (_sz, [_i] * 4),
     "b200_grouped_gemm_nvfp4": (_i, [_i] + [_vp] * 6 + [_vp, _sz, _vp, _i, _vp]),

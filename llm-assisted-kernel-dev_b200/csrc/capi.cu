@@ -161,6 +161,7 @@ int device_state(int device, DeviceState** out) {
                               smem_bytes_persistent<Mode::Group256, kG256Stages>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDual>, pair_smem_bytes<PairDual>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualStreamK>, pair_smem_bytes<PairDualStreamK>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualGather>, pair_smem_bytes<PairDualGather>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualNarrow>, pair_smem_bytes<PairDualNarrow>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairGrouped>, pair_smem_bytes<PairGrouped>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualQuant>, pair_smem_bytes<PairDualQuant>()))) return rc;
@@ -545,6 +546,61 @@ int b200_dual_gemm_nvfp4_quant(const void* a, const void* b1, const void* b2, co
     // `q` stands in for c in the shared argument checks (same alignment rule); it is never written as fp16
     return dual_gemm_impl(a, b1, b2, sfa, sfb1, sfb2, q, m, n, k, 1, n, 0, 0, 0, B200_VARIANT_AUTO, nullptr, 0, stream,
                           device, status, q, sf);
+}
+
+int b200_dual_gemm_nvfp4_gather(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,
+                                const void* sfb2, void* const* c_ranks, int world, int rank, int m, int n_local, int n_total,
+                                int col_offset, int k, void* stream, int device, uint32_t* status) {
+    if (!c_ranks) return fail(B200_E_NULL, "dual gemm (gather): c_ranks is NULL");
+    if (world < 1 || world > 8) return fail(B200_E_LIMIT, "dual gemm (gather): world=%d must be in 1..8", world);
+    if (rank < 0 || rank >= world) return fail(B200_E_SHAPE, "dual gemm (gather): rank=%d is not in [0, %d)", rank, world);
+    for (int r = 0; r < world; ++r) {
+        if (!c_ranks[r]) return fail(B200_E_NULL, "dual gemm (gather): the C pointer of rank %d is NULL", r);
+        if (!aligned16(c_ranks[r])) return fail(B200_E_ALIGN, "dual gemm (gather): the C pointer of rank %d is not 16-byte aligned", r);
+    }
+    if (m > 0 && m % 256) return fail(B200_E_SHAPE, "dual gemm (gather): m=%d is not a multiple of 256 (CTA-pair kernel)", m);
+    if (n_total <= 0 || n_total % 128 || col_offset < 0 || col_offset % 128 || col_offset + n_local > n_total)
+        return fail(B200_E_SHAPE, "dual gemm (gather): columns [%d, %d) do not fit a C of %d columns in 128-column steps",
+                    col_offset, col_offset + n_local, n_total);
+    int rc = validate_dual(a, b1, b2, sfa, sfb1, sfb2, c_ranks[rank], m, n_local, k, 1, n_total,
+                           static_cast<long long>(m) * n_total, static_cast<long long>(n_local) * (k / 2),
+                           static_cast<long long>(n_local / 128) * (k / 64) * 512);
+    if (rc) return rc;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+    DenseProblem p;
+    memset(&p, 0, sizeof p);
+    // no cache: three operand maps and `world` output maps are encoded per call (a few microseconds)
+    if ((rc = encode_operand_map(&p.map_a, a, m, k, 1, static_cast<long long>(m) * (k / 2)))) return rc;
+    if ((rc = encode_operand_map(&p.map_b1, b1, n_local, k, 1, static_cast<long long>(n_local) * (k / 2)))) return rc;
+    if ((rc = encode_operand_map(&p.map_b2, b2, n_local, k, 1, static_cast<long long>(n_local) * (k / 2)))) return rc;
+    for (int r = 0; r < world; ++r)
+        if ((rc = encode_output_map(&p.map_c_rank[r], c_ranks[r], m, n_total, 1, n_total, static_cast<long long>(m) * n_total)))
+            return rc;
+    p.map_c = p.map_c_rank[rank];
+    p.gather_world = world;
+    p.gather_col0 = col_offset;
+    p.sfa = static_cast<const uint8_t*>(sfa);
+    p.sfb1 = static_cast<const uint8_t*>(sfb1);
+    p.sfb2 = static_cast<const uint8_t*>(sfb2);
+    p.c = static_cast<__half*>(c_ranks[rank]);
+    p.ldc = n_total;
+    p.c_batch = static_cast<long long>(m) * n_total;
+    p.sfa_batch = static_cast<long long>(m / 128) * (k / 64) * 512;
+    p.sfb_batch = static_cast<long long>(n_local / 128) * (k / 64) * 512;
+    p.m_tiles = m / 128;
+    p.n_tiles = n_local / 128;
+    p.k_tiles = k / 256;
+    p.batches = 1;
+    p.total_tiles = p.m_tiles * p.n_tiles;
+    p.sf_k_atoms = k / 64;
+    p.k_splits = 1;
+    p.status = status ? status : st->status;
+    p.cycles = st->cycles;
+    return launch_pair<PairDualGather>(p, dual_pair_tiles(p), st->sm_count, 0, static_cast<cudaStream_t>(stream));
 }
 
 int b200_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const void* sfa, const void* sfb1,

@@ -94,6 +94,7 @@ struct alignas(64) DenseProblem {
     CUtensorMap map_a, map_b1, map_b2;   // 3-D {k/2 bytes, rows, batch}, box {128, 128, 1}
     CUtensorMap map_c;                   // 3-D {n, m, batch} fp16, box {64, 32, 1}, 128-byte swizzle (pair kernel)
     CUtensorMap map_b1n, map_b2n;        // B1 / B2 with 64-row boxes (narrow pair tiles only)
+    CUtensorMap map_c_rank[8];           // gather variant: the full C of every rank of the node (own and peers')
     const uint8_t* sfa;
     const uint8_t* sfb1;
     const uint8_t* sfb2;
@@ -111,6 +112,7 @@ struct alignas(64) DenseProblem {
     int sf_k_atoms;                      // k / 64
     int k_splits;                        // 1 unless split-k
     int sk_tiles;                        // pair kernel: pair tiles in the stream-k tail (0 = none)
+    int gather_world, gather_col0;       // gather variant: number of ranks, this shard's first column in the full C
     uint32_t* status;
     unsigned long long* cycles;          // CTA 0 stores its clock64 span here (one store per launch)
 };
@@ -468,7 +470,10 @@ __device__ __forceinline__ void epilogue_tile(const Work& w, uint32_t tmem_base,
 // kAddPartial (stream-k head piece): `partial` points at this lane's slice of the fp32 partial
 // sums another CTA pair computed over the rest of the k range, laid out [4-column group][lane][4];
 // they are added to the accumulator values before the activation.
-template <int kBuf, bool kAddPartial = false>
+// kGather (column shard whose result every rank of a node wants): each box is stored `gather_world`
+// times, once into every rank's full C (its own and, through peer-mapped addresses over NVLink, the
+// others'), at this shard's column offset.  Plain TMA stores, no multicast.
+template <int kBuf, bool kAddPartial = false, bool kGather = false>
 __device__ __forceinline__ void epilogue_tile_staged(const DenseProblem& p, const Work& w, uint32_t tmem_base,
                                                      int quad, int lane, uint32_t release_bar, uint32_t staging,
                                                      int c_col, int c_row, bool store, Tracer* tr = nullptr,
@@ -542,8 +547,13 @@ __device__ __forceinline__ void epilogue_tile_staged(const DenseProblem& p, cons
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0 && store) {
-                tma_store_3d(&p.map_c, staging + static_cast<uint32_t>(chunk >> 2) * 4096u, c_col + (chunk >> 2) * 64,
-                             c_row, w.batch);
+                const uint32_t box_addr = staging + static_cast<uint32_t>(chunk >> 2) * 4096u;
+                if constexpr (kGather) {
+                    for (int r = 0; r < p.gather_world; ++r)
+                        tma_store_3d(&p.map_c_rank[r], box_addr, p.gather_col0 + c_col + (chunk >> 2) * 64, c_row, 0);
+                } else {
+                    tma_store_3d(&p.map_c, box_addr, c_col + (chunk >> 2) * 64, c_row, w.batch);
+                }
                 bulk_commit_group();
             }
         }

@@ -75,6 +75,7 @@ struct PairDual {
     static constexpr bool kGrouped = false;
     static constexpr bool kQuantOut = false;
     static constexpr bool kStreamK = false;
+    static constexpr bool kGather = false;
     static constexpr int kBRows = 128;
     static constexpr int kMmaN = 256;
     static constexpr int kStages = 5;
@@ -118,6 +119,13 @@ struct PairDual {
 struct PairDualStreamK : PairDual {
     static constexpr const char* kName = "nvfp4_gemm_pair<PairDualStreamK>";
     static constexpr bool kStreamK = true;
+};
+
+// Column shard of a dual GEMM whose epilogue stores every tile into the full C of every rank of the
+// node (its own and, over NVLink, the peers'): GEMM and all-gather of the shards in one kernel.
+struct PairDualGather : PairDual {
+    static constexpr const char* kName = "nvfp4_gemm_pair<PairDualGather>";
+    static constexpr bool kGather = true;
 };
 
 // Dual GEMM whose epilogue re-quantises its fp16 result to NVFP4 (packed e2m1 + e4m3
@@ -857,9 +865,11 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 }
                 if (done) {
                 } else if (it & 1) {
-                    epilogue_tile_staged<1>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store, tr);
+                    epilogue_tile_staged<1, false, S::kGather>(p, w, tmem_base, warp, lane, release_bar, staging, c_col,
+                                                               c_row, store, tr);
                 } else {
-                    epilogue_tile_staged<0>(p, w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store, tr);
+                    epilogue_tile_staged<0, false, S::kGather>(p, w, tmem_base, warp, lane, release_bar, staging, c_col,
+                                                               c_row, store, tr);
                 }
             }
             trace(2);   // tile stored

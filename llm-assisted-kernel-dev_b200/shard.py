@@ -74,3 +74,38 @@ def gather_dual_output(c_local, n: int, group=None):
              for lo, hi in (column_range(n, r, world) for r in range(world))]
     dist.all_gather(parts, c_local.contiguous(), group=group)
     return torch.cat(parts, dim=1)
+
+
+def dual_gemm_gathered(shard_data, c_rank_ptrs, rank: int, world: int, n_total: int):
+    """Column-sharded dual GEMM whose epilogue writes this rank's columns into the full
+    ``C [M, n_total]`` of every rank (GEMM and all-gather of the shards in one kernel, plain
+    stores over NVLink to peer-mapped buffers; ``b200_dual_gemm_nvfp4_gather``).
+
+    shard_data   the 10-tuple of ``shard_dual_input(data, rank, world)`` (its ``c`` is not used)
+    c_rank_ptrs  device addresses, as seen from this GPU, of every rank's [M, n_total] fp16 buffer
+                 (this rank's own at index ``rank``; the others peer-mapped, e.g. the ``buffer_ptrs``
+                 of a ``torch.distributed._symmetric_memory`` rendezvous)
+    Runs on the current stream and does not synchronise; the gathered C is complete on every rank
+    once all ranks' launches have finished (synchronise, then a barrier).  The reference is
+    single-GPU and has no counterpart."""
+    import ctypes
+
+    import torch
+
+    from . import _lib
+    a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, _c = shard_data
+    if not a.is_cuda:
+        raise ValueError("dual_gemm_gathered needs CUDA tensors (there is no CPU path)")
+    if len(c_rank_ptrs) != world:
+        raise ValueError("one C address per rank is needed")
+    m, k = a.shape[0], a.shape[1] * 2
+    n_local = b1.shape[0]
+    lo, hi = column_range(n_total, rank, world)
+    if hi - lo != n_local:
+        raise ValueError(f"the shard has {n_local} columns, rank {rank} of {world} owns {hi - lo}")
+    ptrs = (ctypes.c_void_p * world)(*[int(x) for x in c_rank_ptrs])
+    dev = a.device
+    code = _lib.load().b200_dual_gemm_nvfp4_gather(a.data_ptr(), b1.data_ptr(), b2.data_ptr(), sfa_p.data_ptr(),
+                                                   sfb1_p.data_ptr(), sfb2_p.data_ptr(), ptrs, world, rank, m, n_local,
+                                                   n_total, lo, k, torch.cuda.current_stream(dev).cuda_stream, dev.index, None)
+    _lib.check(code)

@@ -161,3 +161,22 @@ def test_python_wrappers_validate_layouts(pkg):
     assert fmt.dual_gemm_flops(8192, 14336, 4096) == 1924145348608
     assert fmt.dual_gemm_bytes(8192, 14336, 4096) == 319815680
     assert fmt.dual_gemm_bytes(8192, 1792, 4096) == 56492032
+
+
+def test_gather_entry_point_rejects_bad_arguments(pkg):
+    lib = pkg._lib.load()
+    E = pkg._lib
+    ops = [FAKE + 4096 * i for i in range(6)]
+    two = (ctypes.c_void_p * 2)(FAKE + 65536, FAKE + 131072)
+
+    def call(c_ranks=two, world=2, rank=0, m=256, n_local=128, n_total=256, col=0, k=256):
+        return lib.b200_dual_gemm_nvfp4_gather(*ops, c_ranks, world, rank, m, n_local, n_total, col, k, None, 0, None)
+    assert call(c_ranks=None) == E.E_NULL
+    assert call(world=9) == E.E_LIMIT
+    assert call(rank=2) == E.E_SHAPE
+    assert call(m=128) == E.E_SHAPE and "256" in lib.b200_last_error().decode()
+    assert call(col=64) == E.E_SHAPE
+    assert call(col=256) == E.E_SHAPE                      # columns [256, 384) of a 256-column C
+    assert call(k=300) == E.E_SHAPE
+    assert call(c_ranks=(ctypes.c_void_p * 2)(FAKE, None)) == E.E_NULL
+    assert call(c_ranks=(ctypes.c_void_p * 2)(FAKE, FAKE + 8)) == E.E_ALIGN

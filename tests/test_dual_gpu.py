@@ -233,3 +233,22 @@ def test_pair_kernel_is_deterministic_over_many_launches(pkg):
         assert pkg._lib.read_status(0) == 0
         for d, want in zip(inputs, first):
             assert torch.equal(d[9].view(torch.int16), want.view(torch.int16)), rep
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_shards_gathered_by_the_epilogue(pkg, oracle, world):
+    # the fused GEMM + all-gather entry point with every "rank" on this one GPU: each rank's launch writes its
+    # columns into all `world` full-size C buffers (local ones here, peer-mapped ones on a node)
+    m, n, k = 512, 1024, 512
+    data = pkg.inputs.generate_input(m, n, k, 1, 23, dist="uniform16", device="cuda")
+    full = [torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda") for _ in range(world)]
+    for rank in range(world):
+        shard = pkg.shard.shard_dual_input(data, rank, world)
+        pkg.shard.dual_gemm_gathered(shard, [c.data_ptr() for c in full], rank, world, n)
+    torch.cuda.synchronize()
+    assert pkg._lib.read_status(0) == 0
+    assert "Gather" in pkg._lib.last_kernel()
+    want = _run(pkg, data, V_PAIR)
+    for c in full:
+        assert torch.equal(c.view(torch.int16), want[:, :, 0].view(torch.int16))
+    _check(oracle, data, full[-1].unsqueeze(-1), TOL_NORTH_STAR)
