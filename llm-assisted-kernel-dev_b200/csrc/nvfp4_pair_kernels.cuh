@@ -778,6 +778,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                     }
                     trace(1);   // k-tile ready
                     uint32_t b = buf;
+                    if (!(kTimingProbes && (flags & kFlagSkipMma) && (i & 3)))   // timing probe: MMAs of every fourth k-tile only
 #pragma unroll
                     for (int kb = 0; kb < kKBlocks; ++kb) {
                         if (kb > 0 && kb % TM::kGranule == 0) b = (b + 1 == TM::kBuffers) ? 0u : b + 1;
