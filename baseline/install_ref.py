@@ -35,7 +35,11 @@ FILES = [
 ]
 
 
-def install(reference_root: str = "/root/reference") -> bool:
+# the reference checkout sits beside this repository
+DEFAULT_ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+
+
+def install(reference_root: str = DEFAULT_ROOT) -> bool:
     """Returns True when every file is in place afterwards."""
     if not os.path.isdir(reference_root):
         return all(os.path.exists(os.path.join(DEST, f)) for f in FILES)
@@ -52,5 +56,5 @@ def install(reference_root: str = "/root/reference") -> bool:
 
 
 if __name__ == "__main__":
-    ok = install(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ok = install(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_ROOT)
     print("baseline/_ref", "ready" if ok else "incomplete")

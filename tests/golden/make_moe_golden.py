@@ -29,7 +29,8 @@ def routing_block(reference_root):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    here = os.path.dirname(os.path.abspath(__file__))
+    root = sys.argv[1] if len(sys.argv) > 1 else os.path.join(here, "..", "..", "..", "reference")   # beside this repository
     code = compile(routing_block(root), "moe_fibench_ref.py[routing]", "exec")
     out = {}
     cases = [("e256", 57, 256, 0.0, 2.5, 1), ("e256b", 64, 256, 0.1, 1.0, 2), ("e64", 96, 64, 0.05, 2.5, 3)]

@@ -4,7 +4,7 @@
 
 (cholesky/eval.py:106-113) with the reference's ``generate_input`` drawing on CUDA, its
 ``ref_kernel`` (``torch._scaled_mm``) as the expected value and its ``check_implementation``
-(rtol = atol = 1e-3, dual_gemm/reference.py:200) as the judge, on every test and benchmark
+(rtol = atol = 1e-3, dual_gemm/reference.py:200) as the arbiter, on every test and benchmark
 spec of utils/dual_gemm/task.yml:46-62.  The reference files are taken, unmodified, from
 ``baseline/_ref/`` (baseline/install_ref.py puts them there).  The grouped problem's
 ``reference.py`` is not part of the reference checkout; its four benchmark lists
