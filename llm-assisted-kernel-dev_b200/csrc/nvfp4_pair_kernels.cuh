@@ -686,33 +686,12 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
             PairWalk<S> walk(p, pair, pairs);
             PairPiece pc;
             trace(10);   // producer starts
-            // Grouped: a pair's consecutive tiles usually belong to different groups, and a tensor map that
-            // the TMA unit has to fetch first stalls the whole load stream for about a microsecond.  The
-            // maps of the next tile's group are therefore acquired and prefetched one tile ahead.
-            PairWalk<S> peek(p, pair, pairs);
-            PairPiece nx;
-            int peek_cursor = 0;
-            if (S::kGrouped && operands) peek.next(p, peek_cursor, nx);   // the piece `walk` returns first
             while (ok && walk.next(p, cursor, pc)) {
                 const Work w = S::get(p, pc.tile, rank, cursor);
-                if (S::kGrouped && operands) {
-                    if (w.group != last_group) {   // only the first tile: later groups were acquired a tile ahead
-                        tensormap_acquire(w.map_a);
-                        tensormap_acquire(w.map_blo);
-                        last_group = w.group;
-                    }
-                    if (peek.next(p, peek_cursor, nx)) {
-                        const Work wn = S::get(p, nx.tile, rank, peek_cursor);
-                        if (wn.group != last_group) {
-                            tensormap_acquire(wn.map_a);
-                            tensormap_acquire(wn.map_blo);
-                            if (lane == 0) {
-                                prefetch_tensormap(wn.map_a);
-                                prefetch_tensormap(wn.map_blo);
-                            }
-                            last_group = wn.group;
-                        }
-                    }
+                if (S::kGrouped && operands && w.group != last_group) {   // tensor maps of a new group, written by the host
+                    tensormap_acquire(w.map_a);
+                    tensormap_acquire(w.map_blo);
+                    last_group = w.group;
                 }
                 for (int i = 0; i < pc.kt_count; ++i) {
                     if (!__all_sync(0xffffffffu, mbar_wait<true>(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status,
