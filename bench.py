@@ -490,7 +490,21 @@ def run_extra(torch, pkg, device, peaks, steps, warmup):
         "us_per_launch": us, "kernel": pkg._lib.last_kernel(), "m_min": min(counts), "m_max": max(counts), "zero_groups": counts.count(0),
         "tflops": flops / us / 1e6, "frac_fp4_nominal": flops / us / 1e6 / NOMINAL_FP4_TFLOPS,
         "hbm_gbs": byts / us / 1e3}
+    extra["l2_to_shared_memory_feed"] = run_feed_probe(torch, pkg, device)
     return extra
+
+
+def run_feed_probe(torch, pkg, device):
+    """What the memory system sustains when a kernel does nothing but the GEMMs' kind of loads (TMA from an
+    L2-resident window into shared memory), next to what the dual GEMM draws: 38 KB per k-tile and CTA."""
+    dev = torch.device(device).index or 0
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    rows = []
+    for ctas, share, tiled in ((1, 1, True), (sms, 1, True), (sms, 1, False), (sms, 2, True), (sms, 32, True)):
+        rows.append(pkg._lib.probe_l2_feed(dev, ctas, share, tiled))
+    drawn = (M // 128) * (N // 128) * (K // 256) * 38 * 1024
+    return {"runs": rows, "dual_gemm_bytes_from_l2_per_launch": drawn,
+            "note": "16 KiB copies, 12 in flight per CTA, 4 issuing warps; share = CTAs reading the same tiles at the same time"}
 
 
 def run_ours(args):
@@ -870,6 +884,8 @@ def main():
     ap.add_argument("--quantize", default=None, help="ROWS,K: launch only the activation quantiser (profiler captures)")
     ap.add_argument("--moe-layer", action="store_true",
                     help="run only the MoE layer steps (routing, plan, gather, grouped GEMM, combine; profiler captures, one GPU)")
+    ap.add_argument("--feed-probe", action="store_true",
+                    help="only measure how fast TMA loads fill shared memory from L2 (one JSON line)")
     ap.add_argument("--grouped", default=None, choices=["g8", "moe"],
                     help="launch only the G=8 or the 64-expert grouped GEMM (profiler captures, one GPU)")
     args = ap.parse_args()
@@ -892,6 +908,11 @@ def main():
         pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
         print(json.dumps({"workload": "moe_layer_t8192_e64_n2048_k7168",
                           **run_moe(torch, pkg, "cuda:0", load_peaks(), args.steps, args.warmup)}), flush=True)
+    elif args.feed_probe:
+        import torch
+        torch.cuda.set_device(0)
+        pkg = importlib.import_module("llm-assisted-kernel-dev_b200")
+        print(json.dumps({"workload": "l2_to_shared_memory_feed", **run_feed_probe(torch, pkg, "cuda:0")}), flush=True)
     elif args.grouped:
         run_grouped_only(args)
     elif args.quantize:

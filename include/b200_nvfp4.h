@@ -346,6 +346,20 @@ int b200_read_status(int device, void* stream, uint32_t* out);
  * (group_gemm/group_gemm_cute4.py:67-79, 622-637). */
 int b200_read_last_cycles(int device, void* stream, uint64_t* out);
 
+/* Measurement aid for the roofline of the GEMMs above: a kernel that does nothing
+ * but TMA loads into shared memory (twelve 16 KiB slots in flight per CTA, four
+ * issuing warps) from a 32 MiB window that stays in L2, on `ctas` CTAs of which
+ * `share` consecutive ones read the same tiles at about the same time.  tiled != 0
+ * loads 128-row x 128-byte boxes with the 128-byte swizzle, as the GEMMs' operand
+ * loads do; 0 loads contiguous 16 KiB.  Allocates and frees its own device memory,
+ * runs on the default stream and synchronises.  Returns the aggregate rate in
+ * TB/s, the bytes per SM clock of the slowest CTA and (optionally, may be NULL)
+ * the SM clock in MHz during the run.  The reference has no counterpart; its
+ * authors reason about the same feed with in-kernel clock64 probes
+ * (group_gemm/group_gemm_cute4.py:67-79). */
+int b200_probe_l2_feed(int device, int ctas, int share, int tiled, int copies_per_cta, double* tb_per_s,
+                       double* bytes_per_clk_per_sm, double* sm_mhz);
+
 /* Name of the kernel the most recent launch of this process used (which one the
  * library's shape heuristic picked), e.g. "nvfp4_gemm_pair<PairDual>". */
 const char* b200_last_kernel(void);

@@ -55,6 +55,8 @@ SIGNATURES = {
     "b200_moe_combine": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _i64, _vp, _i]),
     "b200_read_status": (_i, [_i, _vp, _u32p]),
     "b200_read_last_cycles": (_i, [_i, _vp, ctypes.POINTER(ctypes.c_uint64)]),
+    "b200_probe_l2_feed": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double),
+                                ctypes.POINTER(ctypes.c_double)]),
     "b200_grouped_workspace_forget": (_i, [_i, _vp]),
 }
 
@@ -117,6 +119,16 @@ def last_launch_cycles(device: int, stream: int = 0) -> int:
     out = ctypes.c_uint64(0)
     check(load().b200_read_last_cycles(device, stream, ctypes.byref(out)))
     return int(out.value)
+
+
+def probe_l2_feed(device: int, ctas: int, share: int = 1, tiled: bool = True, copies_per_cta: int = 8000) -> dict:
+    """Rate at which TMA loads alone fill shared memory from L2 (``b200_probe_l2_feed``): aggregate TB/s,
+    bytes per SM clock of the slowest CTA, SM clock during the run."""
+    tbs, bpc, mhz = ctypes.c_double(0), ctypes.c_double(0), ctypes.c_double(0)
+    check(load().b200_probe_l2_feed(device, ctas, share, 1 if tiled else 0, copies_per_cta, ctypes.byref(tbs),
+                                    ctypes.byref(bpc), ctypes.byref(mhz)))
+    return {"ctas": ctas, "share": share, "tiled": bool(tiled), "tb_per_s": tbs.value,
+            "bytes_per_clk_per_sm": bpc.value, "sm_mhz": mhz.value}
 
 
 def last_kernel() -> str:

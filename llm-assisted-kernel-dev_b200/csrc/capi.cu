@@ -15,6 +15,7 @@
 #include "nvfp4_pair_kernels.cuh"
 #include "nvfp4_quantize.cuh"
 #include "moe_kernels.cuh"
+#include "feed_probe.cuh"
 
 namespace b200 {
 namespace {
@@ -1243,6 +1244,73 @@ int b200_quantize_nvfp4(const void* x, int dtype, int rows, int k, int64_t ldx, 
     B200_CUDA(cudaGetLastError());
     ++g_launches;
     g_last_kernel = "nvfp4_quantize";
+    return 0;
+}
+
+int b200_probe_l2_feed(int device, int ctas, int share, int tiled, int copies_per_cta, double* tb_per_s,
+                       double* bytes_per_clk_per_sm, double* sm_mhz) {
+    if (!tb_per_s || !bytes_per_clk_per_sm) return fail(B200_E_NULL, "probe_l2_feed: an output pointer is NULL");
+    if (ctas < 1 || ctas > 1024 || share < 1 || copies_per_cta < kFeedSlots)
+        return fail(B200_E_SHAPE, "probe_l2_feed: ctas=%d share=%d copies_per_cta=%d", ctas, share, copies_per_cta);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    int rc;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+    constexpr int kRows = 16384, kRowBytes = 2048;            // 32 MiB: stays in L2
+    uint8_t* window = nullptr;
+    unsigned long long* cycles = nullptr;
+    B200_CUDA(cudaMalloc(&window, static_cast<size_t>(kRows) * kRowBytes));
+    if (cudaMalloc(&cycles, static_cast<size_t>(ctas) * sizeof(unsigned long long)) != cudaSuccess) {
+        cudaFree(window);
+        return fail(static_cast<int>(cudaErrorMemoryAllocation), "probe_l2_feed: out of device memory");
+    }
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    auto cleanup = [&]() {
+        if (e0) cudaEventDestroy(e0);
+        if (e1) cudaEventDestroy(e1);
+        cudaFree(cycles);
+        cudaFree(window);
+    };
+    FeedProbe p;
+    memset(&p, 0, sizeof p);
+    rc = encode_operand_map(&p.map, window, kRows, kRowBytes * 2, 1, static_cast<long long>(kRows) * kRowBytes);
+    if (rc) { cleanup(); return rc; }
+    p.window = window;
+    p.rows = kRows;
+    p.row_bytes = kRowBytes;
+    constexpr int kMine = kFeedSlots / kFeedIssuers;
+    p.copies_per_issuer = (copies_per_cta / kFeedIssuers + kMine - 1) / kMine * kMine;
+    p.share = share;
+    p.tiled = tiled ? 1 : 0;
+    p.cycles = cycles;
+    p.status = st->status;
+    const size_t smem = static_cast<size_t>(kFeedSlots) * kFeedSlotBytes + 1024;
+    float ms = 0.f;
+    std::vector<unsigned long long> host(ctas);
+    cudaError_t err = cudaMemset(window, 0x11, static_cast<size_t>(kRows) * kRowBytes);
+    if (err == cudaSuccess) err = cudaFuncSetAttribute(l2_feed_probe, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err == cudaSuccess) err = cudaEventCreate(&e0);
+    if (err == cudaSuccess) err = cudaEventCreate(&e1);
+    for (int rep = 0; rep < 2 && err == cudaSuccess; ++rep) {   // the first pass brings the window into L2
+        cudaEventRecord(e0, nullptr);
+        l2_feed_probe<<<ctas, kFeedThreads, smem, nullptr>>>(p);
+        cudaEventRecord(e1, nullptr);
+        err = cudaEventSynchronize(e1);
+        if (err == cudaSuccess) err = cudaGetLastError();
+    }
+    if (err == cudaSuccess) err = cudaEventElapsedTime(&ms, e0, e1);
+    if (err == cudaSuccess) err = cudaMemcpy(host.data(), cycles, host.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+    cleanup();
+    if (err != cudaSuccess) return fail(static_cast<int>(err), "probe_l2_feed: %s", cudaGetErrorString(err));
+    ++g_launches;
+    unsigned long long slowest = 1;
+    for (unsigned long long v : host) slowest = v > slowest ? v : slowest;
+    const double bytes_per_cta = static_cast<double>(p.copies_per_issuer) * kFeedIssuers * kFeedSlotBytes;
+    *tb_per_s = bytes_per_cta * ctas / (static_cast<double>(ms) * 1e-3) / 1e12;
+    *bytes_per_clk_per_sm = bytes_per_cta / static_cast<double>(slowest);
+    if (sm_mhz) *sm_mhz = static_cast<double>(slowest) / (static_cast<double>(ms) * 1e3);
     return 0;
 }
 

@@ -180,3 +180,13 @@ def test_gather_entry_point_rejects_bad_arguments(pkg):
     assert call(k=300) == E.E_SHAPE
     assert call(c_ranks=(ctypes.c_void_p * 2)(FAKE, None)) == E.E_NULL
     assert call(c_ranks=(ctypes.c_void_p * 2)(FAKE, FAKE + 8)) == E.E_ALIGN
+
+
+def test_feed_probe_rejects_bad_arguments(pkg):
+    import ctypes
+    lib = pkg._lib.load()
+    a, b = ctypes.c_double(0), ctypes.c_double(0)
+    assert lib.b200_probe_l2_feed(0, 148, 1, 1, 1200, None, ctypes.byref(b), None) == pkg._lib.E_NULL
+    assert lib.b200_probe_l2_feed(0, 0, 1, 1, 1200, ctypes.byref(a), ctypes.byref(b), None) == pkg._lib.E_SHAPE
+    assert lib.b200_probe_l2_feed(0, 148, 0, 1, 1200, ctypes.byref(a), ctypes.byref(b), None) == pkg._lib.E_SHAPE
+    assert lib.b200_probe_l2_feed(0, 148, 1, 1, 3, ctypes.byref(a), ctypes.byref(b), None) == pkg._lib.E_SHAPE

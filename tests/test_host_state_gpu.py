@@ -164,3 +164,17 @@ def test_launch_cycle_counter(pkg):
     pkg.dual_gemm.custom_kernel(d)
     cycles = pkg._lib.last_launch_cycles(0)
     assert 1_000 < cycles < 50_000_000
+
+
+def test_l2_feed_probe_reports_a_plausible_rate(pkg):
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    alone = pkg._lib.probe_l2_feed(0, 1, 1, True, copies_per_cta=1200)
+    every = pkg._lib.probe_l2_feed(0, sms, 2, True, copies_per_cta=1200)
+    bulk = pkg._lib.probe_l2_feed(0, sms, 1, False, copies_per_cta=1200)
+    assert pkg._lib.read_status(0) == 0
+    for r in (alone, every, bulk):
+        assert 20.0 < r["bytes_per_clk_per_sm"] < 400.0, r       # one SM: tens of bytes per clock, not thousands
+        assert 500.0 < r["sm_mhz"] < 2500.0, r
+    assert every["tb_per_s"] > 20 * alone["tb_per_s"]            # the aggregate grows with the SMs used
+    with pytest.raises(ValueError):
+        pkg._lib.probe_l2_feed(0, 0, 1, True)
