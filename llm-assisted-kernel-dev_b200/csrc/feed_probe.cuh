@@ -65,6 +65,8 @@ __global__ void __launch_bounds__(kFeedThreads, 1) l2_feed_probe(const __grid_co
             else
                 bulk_load(base + s * kFeedSlotBytes, p.window + static_cast<size_t>(g) * kFeedSlotBytes, kFeedSlotBytes, bar);
         }
+        if (!ok)
+            for (int i = 0; i < 64; ++i) __nanosleep(2000);   // a wait ran out: let copies in flight land before the CTA ends
     }
     __syncthreads();
     if (threadIdx.x == 0) p.cycles[blockIdx.x] = static_cast<unsigned long long>(clock64() - t0);
