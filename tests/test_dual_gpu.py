@@ -235,7 +235,7 @@ def test_pair_kernel_is_deterministic_over_many_launches(pkg):
             assert torch.equal(d[9].view(torch.int16), want.view(torch.int16)), rep
 
 
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_shards_gathered_by_the_epilogue(pkg, oracle, world):
     # the fused GEMM + all-gather entry point with every "rank" on this one GPU: each rank's launch writes its
     # columns into all `world` full-size C buffers (local ones here, peer-mapped ones on a node)
