@@ -252,3 +252,22 @@ def test_shards_gathered_by_the_epilogue(pkg, oracle, world):
     for c in full:
         assert torch.equal(c.view(torch.int16), want[:, :, 0].view(torch.int16))
     _check(oracle, data, full[-1].unsqueeze(-1), TOL_NORTH_STAR)
+
+
+def test_library_choice_equals_the_serial_kernel_on_random_shapes(pkg, oracle):
+    # whatever kernel the library picks (one CTA per tile, CTA pairs with wide or narrow tiles), its bits are
+    # those of the one-stage serial kernel, and both agree with the oracle
+    gen = torch.Generator().manual_seed(2024)
+    seen = set()
+    for case in range(10):
+        m = 128 * int(torch.randint(1, 9, (1,), generator=gen))
+        n = 128 * int(torch.randint(1, 13, (1,), generator=gen))
+        k = 256 * int(torch.randint(1, 7, (1,), generator=gen))
+        l = 1 if case % 4 else 2
+        data = pkg.inputs.generate_input(m, n, k, l, 100 + case, dist="reference", device="cuda")
+        auto = _run(pkg, data, V_AUTO).clone()
+        seen.add(pkg._lib.last_kernel())
+        serial = _run(pkg, data, V_SERIAL)
+        assert torch.equal(auto.view(torch.int16), serial.view(torch.int16)), (m, n, k, l)
+        _check(oracle, data, serial, TOL_REFERENCE)
+    assert len(seen) >= 2, seen          # the sweep exercised more than one kernel

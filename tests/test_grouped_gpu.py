@@ -194,3 +194,22 @@ def test_pair_kernel_is_deterministic_over_many_launches(pkg):
         for d, want in zip(inputs, first):
             for (_a, _b, c), w in zip(d[0], want):
                 assert torch.equal(c.view(torch.int16), w.view(torch.int16)), rep
+
+
+def test_every_kernel_gives_the_same_bits_on_random_lists(pkg, oracle):
+    # ragged lists (rows from 0 to 700, not multiples of anything) through the library's choice, the one-CTA
+    # kernels and the CTA-pair kernel: one set of bits, and it agrees with the oracle
+    gen = torch.Generator().manual_seed(77)
+    for case in range(6):
+        groups = int(torch.randint(1, 7, (1,), generator=gen))
+        ms = [int(v) for v in torch.randint(0, 701, (groups,), generator=gen)]
+        ns = [256 * int(v) for v in torch.randint(1, 4, (groups,), generator=gen)]
+        ks = [256 * int(v) for v in torch.randint(1, 5, (groups,), generator=gen)]
+        data = pkg.inputs.generate_grouped_input(ms, ns, ks, groups, 300 + case, dist="reference", device="cuda",
+                                                 fill_c=100.0)
+        base = [o.clone() for o in _run(pkg, data, V_SERIAL)]
+        _check(oracle, data, base, TOL_REFERENCE)
+        for variant in (V_AUTO, V_PERSISTENT, V_PAIR):
+            out = _run(pkg, data, variant)
+            for g, (o, w) in enumerate(zip(out, base)):
+                assert torch.equal(o.view(torch.int16), w.view(torch.int16)), (case, variant, g, ms, ns, ks)
