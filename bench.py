@@ -260,6 +260,23 @@ def run_same_box(args):
                                               "GEMM is two of these plus silu*mul"}
     except Exception as exc:  # noqa: BLE001
         out["cublaslt_nvfp4_gemm"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    try:
+        # a second library kernel for the same plain GEMM: the CUTLASS block-scaled GEMM that vLLM ships
+        from vllm import _custom_ops as vops
+        a8, b8 = a2.view(torch.uint8), data[1][:, :, 0].view(torch.uint8)
+        sa2 = sa.view(-1, k // 16) if sa.dim() == 1 else sa
+        sb2 = sb.view(-1, k // 16) if sb.dim() == 1 else sb
+        alpha = torch.ones(1, dtype=torch.float32, device="cuda:0")
+        got = vops.cutlass_scaled_fp4_mm(a8, b8, sa2, sb2, alpha, torch.float16)
+        want = torch._scaled_mm(a2, b2, sa, sb, bias=None, out_dtype=torch.float16)
+        same = bool(torch.equal(torch.nan_to_num(got.float(), posinf=7e4, neginf=-7e4),
+                                torch.nan_to_num(want.float(), posinf=7e4, neginf=-7e4)))
+        us = timed(lambda j: vops.cutlass_scaled_fp4_mm(a8, b8, sa2, sb2, alpha, torch.float16), 1)
+        out["vllm_cutlass_nvfp4_gemm"] = {"shape": [m, n, k], "us_per_gemm": us, "tflops": 2.0 * m * n * k / us / 1e6,
+                                          "equals_cublaslt": same,
+                                          "note": "vllm._custom_ops.cutlass_scaled_fp4_mm, one plain GEMM, fp16 output"}
+    except Exception as exc:  # noqa: BLE001
+        out["vllm_cutlass_nvfp4_gemm"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
     print(json.dumps(out), flush=True)
 
 
