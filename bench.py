@@ -277,6 +277,21 @@ def run_same_box(args):
                                           "note": "vllm._custom_ops.cutlass_scaled_fp4_mm, one plain GEMM, fp16 output"}
     except Exception as exc:  # noqa: BLE001
         out["vllm_cutlass_nvfp4_gemm"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    try:
+        # the activation quantiser beside vLLM's (same buffers for the same consumer, global scale 1)
+        from vllm import _custom_ops as vops
+        rows, kq = 32768, 8192
+        x = (torch.randn(rows, kq, device="cuda:0") * 4).to(torch.bfloat16)
+        one = torch.ones(1, dtype=torch.float32, device="cuda:0")
+        qbytes = rows * kq * 2 + rows * kq // 2 + rows * kq // 16
+        us_theirs = timed(lambda j: vops.scaled_fp4_quant(x, one), 1)
+        us_ours = timed(lambda j: pkg.quantize.quantize_nvfp4(x), 1)
+        out["vllm_nvfp4_quantiser"] = {"shape": [rows, kq], "vllm_us": us_theirs, "this_library_us": us_ours,
+                                       "vllm_gbs": qbytes / us_theirs / 1e3, "this_library_gbs": qbytes / us_ours / 1e3,
+                                       "note": "bf16 in, packed e2m1 + swizzled e4m3 scale factors out; both calls "
+                                               "allocate their outputs"}
+    except Exception as exc:  # noqa: BLE001
+        out["vllm_nvfp4_quantiser"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
     print(json.dumps(out), flush=True)
 
 
