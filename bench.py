@@ -292,6 +292,46 @@ def run_same_box(args):
                                                "allocate their outputs"}
     except Exception as exc:  # noqa: BLE001
         out["vllm_nvfp4_quantiser"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    try:
+        # the 64-expert list beside the CUTLASS grouped block-scaled GEMM that vLLM's fused MoE calls
+        from vllm import _custom_ops as vops
+        experts, n_g, k_g = 64, 2048, 7168
+        counts = pkg.inputs.moe_expert_counts(8192, experts, 8, seed=0)
+        gdata = pkg.inputs.generate_grouped_input(counts, [n_g] * experts, [k_g] * experts, experts, 0, dist="uniform16",
+                                                  device="cuda:0")
+
+        def flat_sf(perm, rows):      # the buffer behind a permuted view: [row tile][k tile][32][4][4]
+            return perm.view(torch.uint8).permute(5, 2, 4, 0, 1, 3).contiguous().view(-1, k_g // 16)
+
+        a_cat = torch.cat([abc[0][:, :, 0].view(torch.uint8) for abc in gdata[0]], dim=0)
+        b_all = torch.stack([abc[1][:, :, 0].view(torch.uint8) for abc in gdata[0]], dim=0)
+        sfa_cat = torch.cat([flat_sf(sf[0], m) for sf, m in zip(gdata[2], counts)], dim=0).view(torch.float8_e4m3fn)
+        sfb_all = torch.stack([flat_sf(sf[1], n_g) for sf in gdata[2]], dim=0).view(torch.float8_e4m3fn)
+        offs = [0]
+        sf_offs = [0]
+        for m_g in counts:
+            offs.append(offs[-1] + m_g)
+            sf_offs.append(sf_offs[-1] + -(-m_g // 128) * 128)
+        expert_offsets = torch.tensor(offs[:-1], dtype=torch.int32, device="cuda:0")     # first row of every expert
+        sf_offsets = torch.tensor(sf_offs[:-1], dtype=torch.int32, device="cuda:0")     # ... in the padded scale factors
+        sizes = torch.tensor([[m_g, n_g, k_g] for m_g in counts], dtype=torch.int32, device="cuda:0")
+        alphas = torch.ones(experts, dtype=torch.float32, device="cuda:0")
+        y = torch.empty((offs[-1], n_g), dtype=torch.float16, device="cuda:0")
+        vops.cutlass_fp4_moe_mm(y, a_cat, b_all, sfa_cat, sfb_all, alphas, sizes, expert_offsets, sf_offsets)
+        ours = pkg.group_gemm.custom_kernel(gdata)
+        torch.cuda.synchronize()
+        ours_cat = torch.cat([c[:, :, 0] for c in ours], dim=0).float()
+        finite = torch.isfinite(ours_cat) & torch.isfinite(y.float())
+        rel = ((ours_cat - y.float()).abs() / (ours_cat.abs() + 1.0))[finite].max().item()
+        us_theirs = timed(lambda j: vops.cutlass_fp4_moe_mm(y, a_cat, b_all, sfa_cat, sfb_all, alphas, sizes,
+                                                            expert_offsets, sf_offsets), 1)
+        us_ours = timed(lambda j: pkg.group_gemm.custom_kernel(gdata), 1)
+        out["vllm_cutlass_nvfp4_grouped_gemm"] = {
+            "list": "64 experts, 8192 tokens top-8 (sum M = 65536), N=2048, K=7168", "vllm_us": us_theirs,
+            "this_library_us": us_ours, "speedup": us_theirs / us_ours, "max_relative_difference": rel,
+            "note": "vllm._custom_ops.cutlass_fp4_moe_mm on the same operands, concatenated the way it wants them"}
+    except Exception as exc:  # noqa: BLE001
+        out["vllm_cutlass_nvfp4_grouped_gemm"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
     print(json.dumps(out), flush=True)
 
 
