@@ -332,6 +332,17 @@ def run_same_box(args):
             "note": "vllm._custom_ops.cutlass_fp4_moe_mm on the same operands, concatenated the way it wants them"}
     except Exception as exc:  # noqa: BLE001
         out["vllm_cutlass_nvfp4_grouped_gemm"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    try:
+        # the routing kernel beside vLLM's fused grouped_topk (8192 tokens, 256 experts in 8 groups, top-8)
+        from vllm import _custom_ops as vops
+        logits = torch.randn((8192, 256), device="cuda:0")
+        bias = torch.randn((256,), device="cuda:0") * 0.1
+        us_theirs = timed(lambda j: vops.grouped_topk(logits, 8, 4, 8, True, 2.5, bias, 1), 1)
+        bufs = pkg.moe.route(logits, bias, 8, 4, 8, 2.5)
+        us_ours = timed(lambda j: pkg.moe.route(logits, bias, 8, 4, 8, 2.5, out=bufs), 1)
+        out["vllm_grouped_topk"] = {"tokens": 8192, "experts": 256, "vllm_us": us_theirs, "this_library_us": us_ours}
+    except Exception as exc:  # noqa: BLE001
+        out["vllm_grouped_topk"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
     print(json.dumps(out), flush=True)
 
 
