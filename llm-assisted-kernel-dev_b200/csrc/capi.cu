@@ -967,11 +967,25 @@ int b200_moe_route(const float* logits, const float* bias, int tokens, int exper
     DeviceGuard guard;
     if ((rc = guard.enter(device))) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    moe_route<<<(tokens + 7) / 8, 256, 0, s>>>(logits, bias, tokens, experts, n_group, topk_group, top_k, routed_scaling,
-                                                 topk_idx, topk_w);
+    // scores in registers when a lane's run of experts and a group's run of lanes are both whole
+    const int per_lane = experts % 32 == 0 ? experts / 32 : 0;
+    const int group_size = experts / n_group;
+    const int lanes_per_group = per_lane > 0 && group_size % per_lane == 0 ? group_size / per_lane : 0;
+    const bool in_registers = (per_lane == 2 || per_lane == 4 || per_lane == 8) && lanes_per_group > 0 &&
+                              (lanes_per_group & (lanes_per_group - 1)) == 0;
+    const dim3 grid((tokens + 7) / 8);
+    if (in_registers && per_lane == 2)
+        moe_route_regs<2><<<grid, 256, 0, s>>>(logits, bias, tokens, n_group, topk_group, top_k, routed_scaling, topk_idx, topk_w);
+    else if (in_registers && per_lane == 4)
+        moe_route_regs<4><<<grid, 256, 0, s>>>(logits, bias, tokens, n_group, topk_group, top_k, routed_scaling, topk_idx, topk_w);
+    else if (in_registers)
+        moe_route_regs<8><<<grid, 256, 0, s>>>(logits, bias, tokens, n_group, topk_group, top_k, routed_scaling, topk_idx, topk_w);
+    else
+        moe_route<<<grid, 256, 0, s>>>(logits, bias, tokens, experts, n_group, topk_group, top_k, routed_scaling, topk_idx,
+                                       topk_w);
     B200_CUDA(cudaGetLastError());
     ++g_launches;
-    g_last_kernel = "moe_route";
+    g_last_kernel = in_registers ? "moe_route_regs" : "moe_route";
     return 0;
 }
 

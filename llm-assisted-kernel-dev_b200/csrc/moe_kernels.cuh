@@ -116,6 +116,100 @@ __global__ void __launch_bounds__(256) moe_route(const float* __restrict__ logit
     }
 }
 
+// The same routing with the token's scores in registers: lane l of the token's warp holds the kPerLane
+// consecutive experts [l * kPerLane, (l + 1) * kPerLane), so a group of experts is a run of
+// `lanes_per_group` = group_size / kPerLane lanes (a power of two) and nothing is re-read from shared memory
+// for the group scores or for any of the top_k picks.  For experts == 32 * kPerLane, group_size % kPerLane == 0
+// and lanes_per_group a power of two; same picks, same order, same ties (smaller index) as moe_route.
+template <int kPerLane>
+__global__ void __launch_bounds__(256) moe_route_regs(const float* __restrict__ logits, const float* __restrict__ bias,
+                                                      int tokens, int n_group, int topk_group, int top_k, float scale,
+                                                      int* __restrict__ topk_idx, float* __restrict__ topk_w) {
+    constexpr int kExperts = 32 * kPerLane;
+    const int lane = threadIdx.x & 31;
+    const int token = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (token >= tokens) return;
+    float sig[kPerLane], wb[kPerLane];
+    const float* row = logits + static_cast<long long>(token) * kExperts + lane * kPerLane;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+        const float s = 1.0f / (1.0f + expf(-row[j]));
+        sig[j] = s;
+        wb[j] = s + (bias ? bias[lane * kPerLane + j] : 0.0f);
+    }
+    // the two largest biased scores of this lane's experts, then of its group (duplicates count twice)
+    float a = -FLT_MAX, b = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+        const float v = wb[j];
+        if (v > a) {
+            b = a;
+            a = v;
+        } else if (v > b) {
+            b = v;
+        }
+    }
+    const int group_size = kExperts / n_group;
+    const int lanes_per_group = group_size / kPerLane;
+    for (int off = 1; off < lanes_per_group; off <<= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, a, off);
+        const float ob = __shfl_xor_sync(0xffffffffu, b, off);
+        if (a >= oa) {
+            b = fmaxf(b, oa);
+        } else {
+            b = fmaxf(ob, a);
+            a = oa;
+        }
+    }
+    const float total = group_size >= 2 ? a + b : a;
+    // lane g ranks group g, whose lanes start at g * lanes_per_group
+    float gscore = __shfl_sync(0xffffffffu, total, (lane < n_group ? lane : 0) * lanes_per_group);
+    if (lane >= n_group) gscore = -FLT_MAX;
+    uint32_t group_mask = 0;
+    for (int r = 0; r < topk_group; ++r) {
+        float v = gscore;
+        int g = lane;
+        warp_argmax(v, g);
+        group_mask |= 1u << g;
+        if (lane == g) gscore = -FLT_MAX;
+    }
+    if (!((group_mask >> (lane / lanes_per_group)) & 1u)) {
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) wb[j] = -FLT_MAX;    // like the reference's finfo.min fill
+    }
+    float wsum = 0.0f, my_w = 0.0f;
+    int my_e = 0;
+    for (int r = 0; r < top_k; ++r) {
+        float v = wb[0];
+        int best = lane * kPerLane;
+#pragma unroll
+        for (int j = 1; j < kPerLane; ++j)
+            if (wb[j] > v) {
+                v = wb[j];
+                best = lane * kPerLane + j;
+            }
+        warp_argmax(v, best);
+        const int owner = best / kPerLane, bj = best % kPerLane;
+        float s = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j)
+            if (j == bj) {
+                s = sig[j];
+                if (lane == owner) wb[j] = -INFINITY;    // taken
+            }
+        s = __shfl_sync(0xffffffffu, s, owner);
+        wsum += s;
+        if (lane == r) {
+            my_e = best;
+            my_w = s;
+        }
+    }
+    if (lane < top_k) {
+        topk_idx[static_cast<long long>(token) * top_k + lane] = my_e;
+        topk_w[static_cast<long long>(token) * top_k + lane] = my_w / (wsum + 1e-20f) * scale;
+    }
+}
+
 // Counting sort, step 1: block b counts the experts of entries [b * kMoeChunk, (b + 1) * kMoeChunk).
 __global__ void __launch_bounds__(kMoeChunk) moe_count(const int* __restrict__ topk_idx, int entries, int experts,
                                                        int* __restrict__ block_counts) {
