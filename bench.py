@@ -447,12 +447,14 @@ def run_moe(torch, pkg, device, peaks, steps, warmup):
                                             buf.row_offsets.data_ptr(), buf.sfa_atom_offsets.data_ptr(),
                                             buf.row_of.data_ptr(), buf.src_token.data_ptr(), buf.scratch.data_ptr(),
                                             buf.scratch.numel(), stream, dev),
-        "gather_quantize": lambda i: lib.b200_moe_gather_quantize(x.data_ptr(), pkg._lib.DTYPE_BF16, tokens, k, x.stride(0),
-                                                                  buf.src_token.data_ptr(), buf.row_offsets.data_ptr(),
-                                                                  buf.sfa_atom_offsets.data_ptr(), experts, top_k,
-                                                                  buf.a_q.data_ptr(), buf.sfa.data_ptr(),
-                                                                  buf.gather_scratch.data_ptr(), buf.gather_scratch.numel(),
-                                                                  stream, dev),
+        "quantize_scatter": lambda i: lib.b200_moe_quantize_scatter(x.data_ptr(), pkg._lib.DTYPE_BF16, tokens, k, x.stride(0),
+                                                                    buf.row_of.data_ptr(), buf.row_offsets.data_ptr(),
+                                                                    buf.sfa_atom_offsets.data_ptr(), experts, top_k,
+                                                                    buf.a_q.data_ptr(), buf.sfa.data_ptr(), stream, dev),
+        "gather_quantize_two_pass": lambda i: lib.b200_moe_gather_quantize(
+            x.data_ptr(), pkg._lib.DTYPE_BF16, tokens, k, x.stride(0), buf.src_token.data_ptr(), buf.row_offsets.data_ptr(),
+            buf.sfa_atom_offsets.data_ptr(), experts, top_k, buf.a_q.data_ptr(), buf.sfa.data_ptr(),
+            buf.gather_scratch.data_ptr(), buf.gather_scratch.numel(), stream, dev),
         "grouped_gemm": lambda i: lib.b200_moe_grouped_gemm_nvfp4(experts, buf.a_q.data_ptr(), buf.sfa.data_ptr(), rows,
                                                                   weights.b_ptrs, weights.sfb_ptrs, n, k,
                                                                   buf.counts.data_ptr(), buf.row_offsets.data_ptr(),
@@ -465,7 +467,9 @@ def run_moe(torch, pkg, device, peaks, steps, warmup):
     algo = {"route": tokens * experts * 4 + rows * 8,
             # quantise every token once (2 B in, 9/16 B out per element), then read and write 9/16 B per element of
             # every permuted row
-            "gather_quantize": tokens * k * 2 + tokens * (k // 2 + k // 16) + 2 * rows * (k // 2 + k // 16),
+            "gather_quantize_two_pass": tokens * k * 2 + tokens * (k // 2 + k // 16) + 2 * rows * (k // 2 + k // 16),
+            # read every token once (2 B per element), write 9/16 B per element of every permuted row
+            "quantize_scatter": tokens * k * 2 + rows * (k // 2 + k // 16),
             "combine": rows * n * 2 + tokens * n * 2 + rows * 8}
     res = {}
     for name, fn in steps_of.items():
@@ -478,8 +482,9 @@ def run_moe(torch, pkg, device, peaks, steps, warmup):
     sec, _, _ = time_launches(torch, run, steps, warmup, lambda: None)
     res["whole_layer_us"] = sec / steps * 1e6
     res["grouped_gemm"]["tflops"] = 2.0 * rows * n * k / res["grouped_gemm"]["us"] / 1e6
-    res["note"] = ("gather_quantize = one quantisation pass over the tokens + one copy of every quantised row to its "
-                   "top_k places; no step reads anything back to the host")
+    res["note"] = ("quantize_scatter (what the layer runs) = every token row read and quantised once and written straight "
+                   "to its top_k rows; gather_quantize_two_pass = the older entry point (quantise into scratch, then copy "
+                   "every quantised row to its top_k places); no step reads anything back to the host")
     return res
 
 

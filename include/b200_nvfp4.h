@@ -311,6 +311,17 @@ int b200_moe_gather_quantize(const void* x, int dtype, int tokens, int k, int64_
                              void* sfa, void* scratch, size_t scratch_bytes, void* stream,
                              int device);
 
+/* b200_moe_quantize_scatter: the same a_q and sfa as b200_moe_gather_quantize in one
+ *   kernel and without scratch memory, from the token's side: every token's row is read
+ *   and quantised once and each 16-k block is written straight to the token's top_k rows
+ *   row_of[token, slot] of the permuted order (tokens * k * (2 + top_k * 9/16) bytes of
+ *   traffic instead of an intermediate buffer and a second pass).  The reference permutes
+ *   with torch indexing (moe/moe_fibench_ref.py:142-151); it has no quantising step. */
+int b200_moe_quantize_scatter(const void* x, int dtype, int tokens, int k, int64_t ldx,
+                              const int32_t* row_of, const int32_t* row_offsets,
+                              const int32_t* sfa_atom_offsets, int experts, int top_k, void* a_q,
+                              void* sfa, void* stream, int device);
+
 /* b200_moe_grouped_gemm_nvfp4: y[rows of expert e, :] = a_q[rows of e, :] . B_e^T for all
  *   experts in one launch (fp16 y [total_rows, n]).  b / sfb: host arrays of device
  *   pointers to each expert's [n, k/2] packed e2m1 weights and reordered scale factors.

@@ -50,6 +50,7 @@ SIGNATURES = {
     "b200_moe_sfa_bytes": (_sz, [_i, _i, _i, _i]),
     "b200_moe_gather_scratch_bytes": (_sz, [_i, _i]),
     "b200_moe_gather_quantize": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp, _i]),
+    "b200_moe_quantize_scatter": (_i, [_vp, _i, _i, _i, _i64, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _i]),
     "b200_moe_gemm_workspace_bytes": (_sz, [_i]),
     "b200_moe_grouped_gemm_nvfp4": (_i, [_i, _vp, _vp, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp, _i, _vp]),
     "b200_moe_combine": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _i64, _vp, _i]),

@@ -1078,6 +1078,44 @@ int b200_moe_gather_quantize(const void* x, int dtype, int tokens, int k, int64_
     return 0;
 }
 
+int b200_moe_quantize_scatter(const void* x, int dtype, int tokens, int k, int64_t ldx, const int32_t* row_of,
+                              const int32_t* row_offsets, const int32_t* sfa_atom_offsets, int experts, int top_k,
+                              void* a_q, void* sfa, void* stream, int device) {
+    int rc = moe_check_shape("moe quantize+scatter", tokens, experts, top_k);
+    if (rc) return rc;
+    if (!x || !row_of || !row_offsets || !sfa_atom_offsets || !a_q || !sfa)
+        return fail(B200_E_NULL, "moe quantize+scatter: NULL tensor pointer");
+    if (dtype != B200_DTYPE_F16 && dtype != B200_DTYPE_BF16)
+        return fail(B200_E_VARIANT, "moe quantize+scatter: dtype %d is neither B200_DTYPE_F16 nor B200_DTYPE_BF16", dtype);
+    if (k <= 0 || k % 64) return fail(B200_E_SHAPE, "moe quantize+scatter: k=%d is not a positive multiple of 64", k);
+    if (ldx < k || ldx % 8)
+        return fail(B200_E_ALIGN, "moe quantize+scatter: ldx=%lld must be >= k and a multiple of 8", (long long)ldx);
+    if (!aligned16(x) || !aligned16(a_q) || !aligned16(sfa))
+        return fail(B200_E_ALIGN, "moe quantize+scatter: every tensor pointer must be 16-byte aligned");
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceGuard guard;
+    if ((rc = guard.enter(device))) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(device, &st))) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    long long blocks = (static_cast<long long>(tokens) * kMoeScatterSplit + 7) / 8;   // kMoeScatterSplit warps per token
+    const long long cap = static_cast<long long>(st->sm_count) * 32;
+    if (blocks > cap) blocks = cap;
+    const uint16_t* src = static_cast<const uint16_t*>(x);
+    if (dtype == B200_DTYPE_F16)
+        moe_quantize_scatter<kQuantDtypeF16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            src, ldx, tokens, k, row_of, row_offsets, sfa_atom_offsets, experts, top_k, static_cast<uint8_t*>(a_q),
+            static_cast<uint8_t*>(sfa));
+    else
+        moe_quantize_scatter<kQuantDtypeBF16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(
+            src, ldx, tokens, k, row_of, row_offsets, sfa_atom_offsets, experts, top_k, static_cast<uint8_t*>(a_q),
+            static_cast<uint8_t*>(sfa));
+    B200_CUDA(cudaGetLastError());
+    ++g_launches;
+    g_last_kernel = "moe_quantize_scatter";
+    return 0;
+}
+
 size_t b200_moe_gemm_workspace_bytes(int experts) {
     if (experts <= 0) return 0;
     return static_cast<size_t>(experts) * sizeof(GroupEntry) + 256;      // table + the tile count

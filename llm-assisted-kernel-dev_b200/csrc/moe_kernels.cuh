@@ -24,6 +24,10 @@ namespace b200 {
 
 constexpr int kMoeMaxExperts = 256;
 constexpr int kMoeChunk = 1024;          // (token, slot) entries per block of the counting sort
+#ifndef B200_MOE_SCATTER_SPLIT
+#define B200_MOE_SCATTER_SPLIT 4
+#endif
+constexpr int kMoeScatterSplit = B200_MOE_SCATTER_SPLIT;   // warps that share one token in moe_quantize_scatter
 
 // Largest value in the warp and the smallest index that holds it.
 __device__ __forceinline__ void warp_argmax(float& val, int& idx) {
@@ -382,6 +386,70 @@ __global__ void __launch_bounds__(256) moe_gather_rows(const uint8_t* __restrict
                           (local % 32) * 16 + ((local % 128) / 32) * 4;
         for (int j = lane; j < sf_words; j += 32)     // word j = the four scale factors of 64-k block j
             *reinterpret_cast<uint32_t*>(sf_dst + static_cast<long long>(j) * 512) = __ldg(sf_src + j);
+    }
+}
+
+// Both steps in one pass from the token's side: one warp per token reads the token's row once,
+// quantises it 16 values per lane and writes every 16-k block straight to the token's top_k rows of the
+// permuted order (and its scale factors to those rows' places in their experts' atoms).  The token's
+// 2 * k bytes are read once and nothing goes through an intermediate buffer: tokens * k * (2 + top_k *
+// 9/16) bytes in all.  Lane s < top_k looks up slot s once (row, expert by bisection of the row ranges,
+// byte addresses); the loop over the row's blocks broadcasts them.
+template <int kDtype>
+__global__ void __launch_bounds__(256) moe_quantize_scatter(const uint16_t* __restrict__ x, long long ldx, int tokens, int k,
+                                                            const int* __restrict__ row_of,
+                                                            const int* __restrict__ row_offsets,
+                                                            const int* __restrict__ sfa_atom_offsets, int experts, int top_k,
+                                                            uint8_t* __restrict__ a_q, uint8_t* __restrict__ sfa_all) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = k / 16, rest_k = k / 64;
+    const long long warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+    // kMoeScatterSplit warps share a token (every kMoeScatterSplit-th run of 32 blocks each): more loads in flight
+    const long long items = static_cast<long long>(tokens) * kMoeScatterSplit;
+    for (long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); item < items;
+         item += warps) {
+        const long long token = item / kMoeScatterSplit;
+        const int part = static_cast<int>(item % kMoeScatterSplit);
+        unsigned long long q_dst = 0, sf_dst = 0;      // of slot `lane`
+        if (lane < top_k) {
+            const int row = row_of[token * top_k + lane];
+            int lo = 0, hi = experts;                   // expert of the row: last e with row_offsets[e] <= row
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (row_offsets[mid] <= row) lo = mid;
+                else hi = mid;
+            }
+            const int local = row - row_offsets[lo];
+            q_dst = reinterpret_cast<unsigned long long>(a_q + static_cast<long long>(row) * (k / 2));
+            sf_dst = reinterpret_cast<unsigned long long>(
+                sfa_all + (static_cast<long long>(sfa_atom_offsets[lo] + local / 128) * rest_k) * 512 + (local % 32) * 16 +
+                ((local % 128) / 32) * 4);
+        }
+        const uint16_t* src_row = x + token * ldx;
+        for (int kb = part * 32 + lane; kb - lane < blocks_per_row; kb += 32 * kMoeScatterSplit) {   // whole warps loop
+            const bool real = kb < blocks_per_row;
+            uint2 packed = make_uint2(0u, 0u);
+            uint32_t sbyte = 0;
+            if (real) {
+                const uint4 a = __ldg(reinterpret_cast<const uint4*>(src_row + kb * 16));
+                const uint4 b = __ldg(reinterpret_cast<const uint4*>(src_row + kb * 16) + 1);
+                sbyte = quantize_block<kDtype>(a, b, packed);
+            }
+            // four consecutive 16-k blocks of a row are one 32-bit word of the scale-factor layout
+            uint32_t word = sbyte;
+            word |= __shfl_down_sync(0xffffffffu, sbyte, 1) << 8;
+            word |= __shfl_down_sync(0xffffffffu, sbyte, 2) << 16;
+            word |= __shfl_down_sync(0xffffffffu, sbyte, 3) << 24;
+            for (int s = 0; s < top_k; ++s) {
+                const unsigned long long qd = __shfl_sync(0xffffffffu, q_dst, s);
+                const unsigned long long sd = __shfl_sync(0xffffffffu, sf_dst, s);
+                if (real) {
+                    *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(qd) + kb * 8) = packed;
+                    if ((lane & 3) == 0)
+                        *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(sd) + static_cast<long long>(kb >> 2) * 512) = word;
+                }
+            }
+        }
     }
 }
 

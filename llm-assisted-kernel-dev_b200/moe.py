@@ -132,10 +132,9 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, bias, weights: MoEWeights
     _lib.check(lib.b200_moe_plan(buf.topk_idx.data_ptr(), tokens, experts, top_k, buf.counts.data_ptr(),
                                  buf.row_offsets.data_ptr(), buf.sfa_atom_offsets.data_ptr(), buf.row_of.data_ptr(),
                                  buf.src_token.data_ptr(), buf.scratch.data_ptr(), buf.scratch.numel(), stream, dev.index))
-    _lib.check(lib.b200_moe_gather_quantize(x.data_ptr(), _dtype_code(x), tokens, k, x.stride(0), buf.src_token.data_ptr(),
-                                            buf.row_offsets.data_ptr(), buf.sfa_atom_offsets.data_ptr(), experts, top_k,
-                                            buf.a_q.data_ptr(), buf.sfa.data_ptr(), buf.gather_scratch.data_ptr(),
-                                            buf.gather_scratch.numel(), stream, dev.index))
+    _lib.check(lib.b200_moe_quantize_scatter(x.data_ptr(), _dtype_code(x), tokens, k, x.stride(0), buf.row_of.data_ptr(),
+                                             buf.row_offsets.data_ptr(), buf.sfa_atom_offsets.data_ptr(), experts, top_k,
+                                             buf.a_q.data_ptr(), buf.sfa.data_ptr(), stream, dev.index))
     _lib.check(lib.b200_moe_grouped_gemm_nvfp4(experts, buf.a_q.data_ptr(), buf.sfa.data_ptr(), tokens * top_k,
                                                weights.b_ptrs, weights.sfb_ptrs, n, k, buf.counts.data_ptr(),
                                                buf.row_offsets.data_ptr(), buf.sfa_atom_offsets.data_ptr(),

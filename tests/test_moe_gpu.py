@@ -115,3 +115,43 @@ def test_moe_layer_8192_tokens_64_experts(pkg, oracle, moe_oracle):
     assert "PairGrouped" in pkg._lib.last_kernel() or "moe_combine" in pkg._lib.last_kernel()
     assert int(buf.counts.sum().item()) == 8192 * 8
     assert oracle.compare(out, want, 1e-2, 1e-2) == []
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("tokens,experts,top_k,k", [(333, 16, 4, 576), (2048, 64, 8, 7168)])
+def test_one_pass_scatter_writes_the_two_pass_bytes(pkg, dtype, tokens, experts, top_k, k):
+    # b200_moe_quantize_scatter against b200_moe_gather_quantize (whose bytes the layer tests check against the
+    # oracle): the same packed rows and the same scale-factor bytes, padding rows of the atoms untouched by both
+    lib = pkg._lib.load()
+    gen = torch.Generator().manual_seed(tokens + k)
+    x = (torch.randn((tokens, k), generator=gen) * 3).to(dtype).cuda()
+    idx = torch.stack([torch.randperm(experts, generator=gen)[:top_k] for _ in range(tokens)]).to(torch.int32).cuda()
+    i32 = dict(dtype=torch.int32, device="cuda")
+    counts, offs, atoms = torch.empty(experts, **i32), torch.empty(experts + 1, **i32), torch.empty(experts + 1, **i32)
+    row_of, src = torch.empty(tokens * top_k, **i32), torch.empty(tokens * top_k, **i32)
+    scratch = torch.empty(lib.b200_moe_plan_scratch_bytes(tokens, experts, top_k), dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    pkg._lib.check(lib.b200_moe_plan(idx.data_ptr(), tokens, experts, top_k, counts.data_ptr(), offs.data_ptr(),
+                                     atoms.data_ptr(), row_of.data_ptr(), src.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                                     stream, 0))
+    code = pkg._lib.DTYPE_F16 if dtype == torch.float16 else pkg._lib.DTYPE_BF16
+    sf_bytes = lib.b200_moe_sfa_bytes(tokens, experts, top_k, k)
+    out = []
+    for one_pass in (False, True):
+        a_q = torch.full((tokens * top_k, k // 2), 0xEE, dtype=torch.uint8, device="cuda")
+        sfa = torch.full((sf_bytes,), 0xDD, dtype=torch.uint8, device="cuda")
+        if one_pass:
+            pkg._lib.check(lib.b200_moe_quantize_scatter(x.data_ptr(), code, tokens, k, x.stride(0), row_of.data_ptr(),
+                                                         offs.data_ptr(), atoms.data_ptr(), experts, top_k, a_q.data_ptr(),
+                                                         sfa.data_ptr(), stream, 0))
+        else:
+            tmp = torch.empty(lib.b200_moe_gather_scratch_bytes(tokens, k), dtype=torch.uint8, device="cuda")
+            pkg._lib.check(lib.b200_moe_gather_quantize(x.data_ptr(), code, tokens, k, x.stride(0), src.data_ptr(),
+                                                        offs.data_ptr(), atoms.data_ptr(), experts, top_k, a_q.data_ptr(),
+                                                        sfa.data_ptr(), tmp.data_ptr(), tmp.numel(), stream, 0))
+        torch.cuda.synchronize()
+        out.append((a_q, sfa))
+    assert pkg._lib.last_kernel() == "moe_quantize_scatter"
+    assert torch.equal(out[0][0], out[1][0])
+    assert torch.equal(out[0][1], out[1][1])
+    assert not torch.all(out[1][1] == 0xDD)
