@@ -441,6 +441,7 @@ def run_moe(torch, pkg, device, peaks, steps, warmup):
     stream = torch.cuda.current_stream().cuda_stream
     dev = torch.cuda.current_device()
     rows = tokens * top_k
+    two_pass_scratch = torch.empty(int(lib.b200_moe_gather_scratch_bytes(tokens, k)), dtype=torch.uint8, device=device)
     steps_of = {
         "route": lambda i: pkg.moe.route(logits, None, 8, 4, top_k, 2.5, out=(buf.topk_idx, buf.topk_w)),
         "plan": lambda i: lib.b200_moe_plan(buf.topk_idx.data_ptr(), tokens, experts, top_k, buf.counts.data_ptr(),
@@ -454,7 +455,7 @@ def run_moe(torch, pkg, device, peaks, steps, warmup):
         "gather_quantize_two_pass": lambda i: lib.b200_moe_gather_quantize(
             x.data_ptr(), pkg._lib.DTYPE_BF16, tokens, k, x.stride(0), buf.src_token.data_ptr(), buf.row_offsets.data_ptr(),
             buf.sfa_atom_offsets.data_ptr(), experts, top_k, buf.a_q.data_ptr(), buf.sfa.data_ptr(),
-            buf.gather_scratch.data_ptr(), buf.gather_scratch.numel(), stream, dev),
+            two_pass_scratch.data_ptr(), two_pass_scratch.numel(), stream, dev),
         "grouped_gemm": lambda i: lib.b200_moe_grouped_gemm_nvfp4(experts, buf.a_q.data_ptr(), buf.sfa.data_ptr(), rows,
                                                                   weights.b_ptrs, weights.sfb_ptrs, n, k,
                                                                   buf.counts.data_ptr(), buf.row_offsets.data_ptr(),

@@ -60,8 +60,6 @@ class _Buffers:
         self.src_token = torch.empty(rows, **i32)
         self.scratch = torch.empty(max(1, int(lib.b200_moe_plan_scratch_bytes(tokens, experts, top_k))),
                                    dtype=torch.uint8, device=dev)
-        self.gather_scratch = torch.empty(max(16, int(lib.b200_moe_gather_scratch_bytes(tokens, k))), dtype=torch.uint8,
-                                          device=dev)
         self.a_q = torch.empty((rows, k // 2), dtype=torch.uint8, device=dev)
         self.sfa = torch.zeros(int(lib.b200_moe_sfa_bytes(tokens, experts, top_k, k)), dtype=torch.uint8, device=dev)
         self.y = torch.empty((rows, n), dtype=torch.float16, device=dev)
