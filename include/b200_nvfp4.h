@@ -203,8 +203,8 @@ int b200_grouped_workspace_forget(int device, const void* workspace);
  * path where cudaMalloc's implicit device synchronisation is unacceptable has
  * nowhere to put the per-group descriptor table that b200_grouped_gemm_nvfp4
  * keeps in the caller's workspace.  Here the table lives in a fixed array inside
- * the library's device image instead: B200_STATIC_MAX_GROUPS entries of 384
- * bytes (24 KiB), present on every GPU that loads the library until the process
+ * the library's device image instead: B200_STATIC_MAX_GROUPS entries of 512
+ * bytes (32 KiB), present on every GPU that loads the library until the process
  * exits.  Arguments and results are those of b200_grouped_gemm_nvfp4 without the
  * workspace.  It always runs the one-CTA-per-tile kernels (128 x 128 or 128 x 256
  * tiles); the workspace entry point additionally picks the CTA-pair kernel for

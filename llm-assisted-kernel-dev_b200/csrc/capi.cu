@@ -165,6 +165,7 @@ int device_state(int device, DeviceState** out) {
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualGather>, pair_smem_bytes<PairDualGather>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualNarrow>, pair_smem_bytes<PairDualNarrow>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairGrouped>, pair_smem_bytes<PairGrouped>()))) return rc;
+        if ((rc = opt_in_smem(nvfp4_gemm_pair<PairGroupedShared>, pair_smem_bytes<PairGroupedShared>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_pair<PairDualQuant>, pair_smem_bytes<PairDualQuant>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Dual>, smem_bytes_serial<Mode::Dual>()))) return rc;
         if ((rc = opt_in_smem(nvfp4_gemm_serial<Mode::Group128>, smem_bytes_serial<Mode::Group128>()))) return rc;
@@ -649,6 +650,8 @@ int build_group_table(GroupEntry* table, int groups, const void* const* a, const
         e.c = static_cast<__half*>(c[g]);
         if ((rc = encode_operand_map(&e.map_a, a[g], m, k, 1, static_cast<long long>(m) * (k / 2)))) return rc;
         if ((rc = encode_operand_map(&e.map_b, b[g], n, k, 1, static_cast<long long>(n) * (k / 2)))) return rc;
+        // the CTA-pair kernel stores through this map: its m rows are the extent, so rows of a tile past them are clipped
+        if (pair && (rc = encode_output_map(&e.map_c, c[g], m, n, 1, n, static_cast<long long>(m) * n))) return rc;
     }
     *total_tiles = tile_begin;
     return 0;
@@ -916,7 +919,7 @@ int b200_grouped_gemm_nvfp4_static(int groups, const void* const* a, const void*
     const int tile_n = (all_n256 && tiles128 / 2 >= 2LL * st->sm_count) ? 256 : 128;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if ((rc = reject_capture(s, "grouped gemm (static table)"))) return rc;
-    // Host copy of the table on the stack (24 KiB at most): nothing is allocated.
+    // Host copy of the table on the stack (32 KiB at most): nothing is allocated.
     GroupEntry table[B200_STATIC_MAX_GROUPS];
     int tile_begin = 0;
     if ((rc = build_group_table(table, groups, a, b, sfa, sfb, c, mnk, tile_n, &tile_begin))) return rc;
@@ -1225,7 +1228,8 @@ int b200_moe_grouped_gemm_nvfp4(int experts, const void* a_q, const void* sfa, i
     p.cycles = st->cycles;
     p.trace = nullptr;
     // full grid: how many tiles there are is only known on the device
-    if (use_pair) return launch_pair<PairGrouped>(p, 1 << 30, st->sm_count, 0, s);
+    // rows past an expert's count are the next expert's: row-predicated stores, not the per-group store maps
+    if (use_pair) return launch_pair<PairGroupedShared>(p, 1 << 30, st->sm_count, 0, s);
     return launch_persistent<Mode::Group128, kG128Stages>(p, 1 << 30, st->sm_count, 0, s);
 }
 

@@ -120,6 +120,8 @@ struct alignas(64) DenseProblem {
 // Grouped GEMM: one entry per group in device memory (the workspace).
 struct alignas(128) GroupEntry {
     CUtensorMap map_a, map_b;            // 3-D {k/2 bytes, rows, 1}
+    CUtensorMap map_c;                   // fp16 C of the group for TMA stores (box 64 columns x 32 rows); rows = m, so
+                                         // a box that reaches past the group's last row is clipped by the TMA unit
     const uint8_t* sfa;
     const uint8_t* sfb;
     __half* c;
@@ -129,7 +131,7 @@ struct alignas(128) GroupEntry {
     int a_row0;                          // first row of this group in map_a (groups that share one A buffer)
     int pad[7];
 };
-static_assert(sizeof(GroupEntry) == 384, "GroupEntry layout");
+static_assert(sizeof(GroupEntry) == 512, "GroupEntry layout");
 
 struct GroupedProblem {
     const GroupEntry* groups;
@@ -150,6 +152,7 @@ struct Work {
     const uint8_t* sfblo;
     const uint8_t* sfbhi;
     __half* c;               // &C(m0, n0)
+    const void* map_c = nullptr;   // grouped CTA-pair tiles: the group's store map
     long long ldc;
     int a_row, blo_row, bhi_row, batch;
     int rows_valid, cols_valid;

@@ -199,6 +199,7 @@ struct PairGrouped {
     using TM = TmemMap<Mode::Group256>;
     static constexpr const char* kName = "nvfp4_gemm_pair<PairGrouped>";
     static constexpr bool kGrouped = true;
+    static constexpr bool kStoreByTma = true;     // C leaves through GroupEntry::map_c, which clips rows past the group's M
     static constexpr bool kQuantOut = false;
     static constexpr bool kStreamK = false;
     static constexpr int kBRows = 128;
@@ -236,6 +237,7 @@ struct PairGrouped {
         w.sfbhi = e->sfb + (2 * n_blk + 1) * sf_row;
         w.ldc = e->ldc;
         w.c = e->c + static_cast<long long>(m_blk) * kTileM * e->ldc + n_blk * 256;
+        w.map_c = &e->map_c;
         const int left = e->m - m_blk * kTileM;
         w.rows_valid = left < 0 ? 0 : (left > kTileM ? kTileM : left);
         w.cols_valid = 256;
@@ -246,6 +248,13 @@ struct PairGrouped {
         w.split = 0;
         return w;
     }
+};
+
+// Groups whose C tiles live in one shared buffer (the MoE layer's y): rows of a tile past a group's count
+// belong to the next group, so the epilogue stores row by row, predicated, instead of by TMA.
+struct PairGroupedShared : PairGrouped {
+    static constexpr const char* kName = "nvfp4_gemm_pair<PairGroupedShared>";
+    static constexpr bool kStoreByTma = false;
 };
 
 // The sequence of pieces of one pair, the same in every role of both CTAs.  Whole tiles are
@@ -359,6 +368,67 @@ __device__ __forceinline__ void epilogue_tile_grouped_pair(const Work& w, uint32
                 if (store && r < rows_here) st_global_v4(dst + static_cast<long long>(r) * w.ldc, a, b, c, d);
             }
             __syncwarp();
+        }
+    }
+}
+
+// The same tile leaving through TMA stores (policies with kStoreByTma): each 64-column slice of the warp's 32 rows is
+// converted into one of the warp's two 4 KB staging boxes and handed to the TMA unit, which clips the rows past the
+// group's M (the store map's extent) by itself.  No shared-memory read-back and no global store instruction runs on
+// the SM's load/store path, which the scale-factor warps and the MMAs' operand reads share with this epilogue.
+template <int kBuf>
+__device__ __forceinline__ void epilogue_tile_grouped_pair_tma(const Work& w, uint32_t tmem_base, int quad, int lane,
+                                                               uint32_t release_bar, uint32_t staging, int c_col, int c_row,
+                                                               bool store) {
+    using TM = TmemMap<Mode::Group256>;
+    constexpr int kEarly = TM::kEarlyChunks;
+    constexpr int kSharedRel = (kBuf == 0) ? TM::kSharedBegin : 0;
+    const uint32_t acc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kBuf * TM::kAccStride;
+    uint32_t early[kEarly][16];
+    static_assert(kEarly == 9, "the shared columns are fetched as 64 + 64 + 16");
+    tc_ld_x64(acc + kSharedRel, &early[0][0]);
+    tc_ld_x64(acc + kSharedRel + 64, &early[4][0]);
+    tc_ld_x16(acc + kSharedRel + 128, early[8]);
+    tc_wait_ld();
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_cluster_relaxed(release_bar);   // barrier of the pair's first CTA
+    const bool rows_exist = w.rows_valid - quad * 32 > 0;       // else every row of this warp lies past the group's M
+    const uint32_t row_base = staging + lane * 128;
+    const uint32_t swz = static_cast<uint32_t>(lane & 7);
+#pragma unroll
+    for (int chunk = 0; chunk < 16; ++chunk) {
+        const int col = chunk * 16;
+        const bool is_early = col >= kSharedRel && col < kSharedRel + kEarly * 16;
+        uint32_t x[16];
+        if (!is_early) {
+            tc_ld_x16(acc + col, x);
+            tc_wait_ld();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = early[(col - kSharedRel) / 16][i];
+        }
+        if ((chunk & 3) == 0) {
+            // the box about to be rewritten was handed to the TMA unit two slices ago (or by the previous tile)
+            if (lane == 0) bulk_wait_group_read_1();
+            __syncwarp();
+        }
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) packed[i] = pack_half2(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
+        const uint32_t box = row_base + static_cast<uint32_t>((chunk >> 2) & 1) * 4096u;
+        const uint32_t u0 = static_cast<uint32_t>((chunk & 3) * 2);
+        st_shared_v4(box + ((u0 ^ swz) << 4), packed[0], packed[1], packed[2], packed[3]);
+        st_shared_v4(box + (((u0 + 1) ^ swz) << 4), packed[4], packed[5], packed[6], packed[7]);
+        if ((chunk & 3) == 3) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                if (store && rows_exist)
+                    tma_store_3d(w.map_c, staging + static_cast<uint32_t>((chunk >> 2) & 1) * 4096u, c_col + (chunk >> 2) * 64,
+                                 c_row, 0);
+                bulk_commit_group();      // an empty group keeps the count of groups per tile at four
+            }
         }
     }
 }
@@ -805,7 +875,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         __syncwarp();
     } else if (warp < 4) {
         // ------------------------------ epilogue (each CTA its own 128 rows)
-        int it = 0, cursor = 0;
+        int it = 0, cursor = 0, epi_group = -1;
         Tracer trace(kTimingProbes && lane == 0 && blockIdx.x == 0 ? p.trace : nullptr, warp == 0 ? 7 : warp);
         Tracer* tr = kTimingProbes ? &trace : nullptr;
         PairWalk<S> walk(p, pair, pairs);
@@ -832,10 +902,22 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
                 else
                     epilogue_tile_quant<0>(p, w, tmem_base, warp, lane, release_bar, m_blk, n_blk, store);
             } else if constexpr (S::kGrouped) {
-                if (it & 1)
-                    epilogue_tile_grouped_pair<1>(w, tmem_base, warp, lane, release_bar, staging, store);
-                else
-                    epilogue_tile_grouped_pair<0>(w, tmem_base, warp, lane, release_bar, staging, store);
+                if constexpr (S::kStoreByTma) {
+                    if (w.group != epi_group) {       // store map of a new group, written by the host
+                        if (lane == 0) tensormap_acquire(w.map_c);
+                        epi_group = w.group;
+                    }
+                    const int c_col = w.blo_row - static_cast<int>(rank) * 128, c_row = w.a_row + warp * 32;
+                    if (it & 1)
+                        epilogue_tile_grouped_pair_tma<1>(w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store);
+                    else
+                        epilogue_tile_grouped_pair_tma<0>(w, tmem_base, warp, lane, release_bar, staging, c_col, c_row, store);
+                } else {
+                    if (it & 1)
+                        epilogue_tile_grouped_pair<1>(w, tmem_base, warp, lane, release_bar, staging, store);
+                    else
+                        epilogue_tile_grouped_pair<0>(w, tmem_base, warp, lane, release_bar, staging, store);
+                }
             } else if constexpr (S::kMmaN == 128) {
                 const int c_col = w.blo_row, c_row = w.a_row + warp * 32;
                 if (it & 1)
@@ -878,7 +960,7 @@ nvfp4_gemm_pair(const __grid_constant__ typename S::Params p, int flags) {
         }
         // the staging area must outlive the TMA unit's reads; the stores themselves are
         // complete at the latest when the grid is
-        if (!S::kGrouped && !S::kQuantOut && lane == 0) bulk_wait_group_read_all();
+        if (!S::kQuantOut && lane == 0) bulk_wait_group_read_all();
         __syncwarp();
     }
     // Nobody leaves while the partner may still signal its barriers or while MMAs

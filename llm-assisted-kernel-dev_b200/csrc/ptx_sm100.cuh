@@ -158,6 +158,10 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 __device__ __forceinline__ void bulk_wait_group_read_all() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// All but the newest of this thread's bulk groups have finished reading shared memory.
+__device__ __forceinline__ void bulk_wait_group_read_1() {
+    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 // All of this thread's bulk groups are complete (their global writes performed).
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 

@@ -143,8 +143,8 @@ def test_split_k_workspace_size(pkg):
 def test_workspace_size(pkg):
     lib = pkg._lib.load()
     assert lib.b200_grouped_workspace_bytes(0) == 0
-    assert lib.b200_grouped_workspace_bytes(1) == 384
-    assert lib.b200_grouped_workspace_bytes(64) == 64 * 384
+    assert lib.b200_grouped_workspace_bytes(1) == 512
+    assert lib.b200_grouped_workspace_bytes(64) == 64 * 512
 
 
 def test_python_wrappers_validate_layouts(pkg):

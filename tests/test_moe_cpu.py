@@ -60,7 +60,7 @@ def test_moe_entry_points_reject_bad_arguments(pkg):
     assert lib.b200_moe_quantize_scatter(FAKE, 5, 16, 128, 128, FAKE, FAKE, FAKE, 64, 8, FAKE, FAKE, None, 0) == E.E_VARIANT
     assert lib.b200_moe_quantize_scatter(FAKE, 0, 16, 128, 128, None, FAKE, FAKE, 64, 8, FAKE, FAKE, None, 0) == E.E_NULL
     assert lib.b200_moe_quantize_scatter(FAKE, 0, 16, 128, 100, FAKE, FAKE, FAKE, 64, 8, FAKE, FAKE, None, 0) == E.E_ALIGN
-    assert lib.b200_moe_gemm_workspace_bytes(64) == 64 * 384 + 256
+    assert lib.b200_moe_gemm_workspace_bytes(64) == 64 * 512 + 256
     assert lib.b200_moe_combine(FAKE, 2050, FAKE, FAKE, 16, 8, 0, FAKE, 2050, None, 0) == E.E_SHAPE
     assert lib.b200_moe_combine(FAKE, 2048, FAKE, FAKE, 16, 8, 7, FAKE, 2048, None, 0) == E.E_VARIANT
 
