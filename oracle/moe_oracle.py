@@ -22,13 +22,20 @@ import torch
 from . import nvfp4_oracle as orc
 
 
-def route(logits: torch.Tensor, bias, n_group: int, topk_group: int, top_k: int, scale: float):
+def route(logits: torch.Tensor, bias, n_group: int, topk_group: int, top_k: int, scale: float,
+          exact_sigmoid: bool = False):
     """Returns (topk_idx [T, top_k] int64, unordered like the reference's, and the dense weight
     matrix [T, E] fp32)."""
     logits = logits.detach().cpu().float()
     t, e = logits.shape
     b = torch.zeros(e) if bias is None else bias.detach().cpu().float().reshape(-1)
-    s = 1.0 / (1.0 + torch.exp(-logits))
+    if exact_sigmoid:
+        # in double precision, rounded to fp32: the correctly rounded value of the reference's fp32 expression
+        # (moe/moe_fibench_ref.py:103), independent of which vectorised fp32 exp the host's torch build dispatches
+        # to (on one machine a large tensor's fp32 exp came back 1e-5 off in about one process out of a dozen)
+        s = (1.0 / (1.0 + torch.exp(-logits.double()))).float()
+    else:
+        s = 1.0 / (1.0 + torch.exp(-logits))      # the reference's expression, bit for bit
     swb = s + b
     group_size = e // n_group
     grouped = swb.view(t, n_group, group_size)
@@ -65,7 +72,7 @@ def moe_forward(x: torch.Tensor, logits, bias, b_list, sfb_list, n_group, topk_g
     x = x.detach().cpu()
     t, k = x.shape
     experts = len(b_list)
-    topk_idx, weights = route(logits, bias, n_group, topk_group, top_k, scale)
+    topk_idx, weights = route(logits, bias, n_group, topk_group, top_k, scale, exact_sigmoid=True)
     _counts, _offsets, tokens_of = plan(topk_idx, experts)
     n = orc.as_u8(b_list[0]).shape[0]
     out = torch.zeros((t, n), dtype=torch.float32)
