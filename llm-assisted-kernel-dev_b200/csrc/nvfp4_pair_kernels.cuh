@@ -462,6 +462,7 @@ __device__ __forceinline__ void epilogue_tile_quant(const DenseProblem& p, const
     // scale factors of this row, columns n_blk*128 ...: k-blocks n_blk*8 + chunk of the (m, n/16) scale matrix
     uint8_t* sf_row = p.sf_out + (static_cast<long long>(m_blk) * (n_total / 64) + n_blk * 2) * 512 + lane * 16 + quad * 4;
     uint32_t sf_word = 0;
+    uint2 held = make_uint2(0u, 0u);
 #pragma unroll
     for (int chunk = 0; chunk < 8; ++chunk) {
         const int xcol = chunk * 16;
@@ -489,7 +490,13 @@ __device__ __forceinline__ void epilogue_tile_quant(const DenseProblem& p, const
         const uint32_t sbyte = quantize_block<kQuantDtypeF16>(make_uint4(h[0], h[1], h[2], h[3]),
                                                               make_uint4(h[4], h[5], h[6], h[7]), packed);
         sf_word |= sbyte << (8 * (chunk & 3));
-        if (store) *reinterpret_cast<uint2*>(q_row + chunk * 8) = packed;
+        // four chunks = 64 columns = 32 packed bytes of the row: one whole 32-byte sector, written with two 16-byte
+        // stores instead of four 8-byte ones
+        if ((chunk & 1) == 0) {
+            held = packed;
+        } else if (store) {
+            st_global_v4(q_row + (chunk - 1) * 8, held.x, held.y, packed.x, packed.y);
+        }
         if ((chunk & 3) == 3) {
             if (store) *reinterpret_cast<uint32_t*>(sf_row + (chunk >> 2) * 512) = sf_word;
             sf_word = 0;
